@@ -1,0 +1,48 @@
+// Shared host/device helpers for the featgraph_b200 kernels.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "featgraph_b200.h"
+
+namespace fg {
+
+// Thread-local error text behind fg_last_error().
+char* error_buffer();
+int fail(int code, const char* fmt, ...);
+
+#define FG_CUDA_TRY(expr)                                                                  \
+    do {                                                                                   \
+        cudaError_t fg_err__ = (expr);                                                     \
+        if (fg_err__ != cudaSuccess)                                                       \
+            return ::fg::fail(FG_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
+                              cudaGetErrorString(fg_err__), __FILE__, __LINE__);           \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int pow2_floor(int v) {
+    int p = 1;
+    while (p * 2 <= v) p *= 2;
+    return p;
+}
+inline int pow2_ceil(int v) {
+    int p = 1;
+    while (p < v) p *= 2;
+    return p;
+}
+
+// 128-bit read-only gather of one feature-row slice.
+__device__ __forceinline__ float4 ldg4(const float* p) {
+    return __ldg(reinterpret_cast<const float4*>(p));
+}
+
+// acc + a*b with two roundings (never contracted into an FMA).
+__device__ __forceinline__ float mul_then_add(float acc, float a, float b) {
+    return __fadd_rn(acc, __fmul_rn(a, b));
+}
+
+}  // namespace fg

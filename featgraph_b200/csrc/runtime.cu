@@ -1,0 +1,50 @@
+// Error text, version and device query of the C ABI.
+#include "common.cuh"
+
+namespace fg {
+
+char* error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+}  // namespace fg
+
+extern "C" {
+
+int fg_version(void) { return 100; }
+
+const char* fg_last_error(void) { return fg::error_buffer(); }
+
+int fg_device_info(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor, int64_t* l2_bytes) {
+    int dev = 0;
+    FG_CUDA_TRY(cudaGetDevice(&dev));
+    int v = 0;
+    if (sm_count) {
+        FG_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev));
+        *sm_count = v;
+    }
+    if (cc_major) {
+        FG_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, dev));
+        *cc_major = v;
+    }
+    if (cc_minor) {
+        FG_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMinor, dev));
+        *cc_minor = v;
+    }
+    if (l2_bytes) {
+        FG_CUDA_TRY(cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev));
+        *l2_bytes = v;
+    }
+    return FG_OK;
+}
+
+}  // extern "C"

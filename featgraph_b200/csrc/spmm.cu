@@ -1,0 +1,279 @@
+// SpMM (CSR and DDS adjacency times dense features, sum aggregation) for sm_100a.
+//
+// Work decomposition.  The unit of work is (feature tile, row): a group of G lanes owns
+// one row's slice of G*VEC output columns (VEC = 4 floats per lane with 128-bit gathers).
+// Each lane keeps its VEC accumulators in registers and walks the row's nonzeros in
+// storage order, so every output element is a strictly sequential fp32 sum - the value
+// the x86 loop nest of the reference produces (python/featgraph/op/vanilla_spmm.py:46-56
+// with the loop order of :73) - and no launch parameter can change a result bit.
+//
+// Memory behaviour.  Units are numbered tile-major: all rows of feature tile 0, then tile
+// 1, ...  While a tile is being processed only the n_cols x (G*VEC*4 B) slice of x is
+// gathered from, and the tile width is chosen so that this slice stays resident in L2;
+// the CSR arrays are then the only DRAM stream.  The G lanes of a group read G*16
+// contiguous bytes per nonzero (one or more full 128-byte lines for G >= 8).  Column
+// indices and values are fetched G at a time, coalesced, one batch ahead of use, and
+// handed round the group with shuffles; the gathers of up to 8 nonzeros are issued
+// before the first of them is consumed.
+//
+// Balance.  Rows are visited in the order of an fg_row_schedule (heaviest first), blocks
+// are launched in that order, and the groups sharing a warp hold neighbouring (hence
+// similar-length) rows, so the warp-uniform loop below wastes few iterations.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+struct SpmmArgs {
+    const int32_t* pos;    // indptr (CSR) or s1_pos (DDS: parts blocks of n_rows+1)
+    const int32_t* idx;    // column ids (DDS: relative to the partition's first column)
+    const float* vals;
+    const float* x;
+    float* out;
+    const int32_t* order;  // row visiting order or nullptr
+    int32_t n_rows;
+    int32_t d;
+    int32_t n_tiles;
+    int32_t parts;          // 1 for CSR
+    int32_t cols_per_part;  // DDS only
+};
+
+template <int VEC>
+struct Slice;
+template <>
+struct Slice<4> {
+    float4 v;
+    __device__ __forceinline__ void load(const float* p) { v = fg::ldg4(p); }
+    __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+    __device__ __forceinline__ void axpy(float a, const Slice& x) {
+        v.x = fg::mul_then_add(v.x, a, x.v.x);
+        v.y = fg::mul_then_add(v.y, a, x.v.y);
+        v.z = fg::mul_then_add(v.z, a, x.v.z);
+        v.w = fg::mul_then_add(v.w, a, x.v.w);
+    }
+    __device__ __forceinline__ void add(const Slice& x) {
+        v.x = __fadd_rn(v.x, x.v.x);
+        v.y = __fadd_rn(v.y, x.v.y);
+        v.z = __fadd_rn(v.z, x.v.z);
+        v.w = __fadd_rn(v.w, x.v.w);
+    }
+    __device__ __forceinline__ void select(bool take, const Slice& x) {
+        v.x = take ? x.v.x : v.x;
+        v.y = take ? x.v.y : v.y;
+        v.z = take ? x.v.z : v.z;
+        v.w = take ? x.v.w : v.w;
+    }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+};
+template <>
+struct Slice<1> {
+    float v;
+    __device__ __forceinline__ void load(const float* p) { v = __ldg(p); }
+    __device__ __forceinline__ void zero() { v = 0.f; }
+    __device__ __forceinline__ void axpy(float a, const Slice& x) { v = fg::mul_then_add(v, a, x.v); }
+    __device__ __forceinline__ void add(const Slice& x) { v = __fadd_rn(v, x.v); }
+    __device__ __forceinline__ void select(bool take, const Slice& x) { v = take ? x.v : v; }
+    __device__ __forceinline__ void store(float* p) const { *p = v; }
+};
+
+// G lanes per (row, tile) unit; VEC floats per lane; DDS selects the two-level sum.
+template <int G, int VEC, bool DDS>
+__global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a) {
+    constexpr int CH = G < 8 ? G : 8;  // gathers issued back to back
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (G - 1);
+    const int64_t unit = (int64_t)blockIdx.x * (kThreads / G) + (threadIdx.x / G);
+    const int64_t n_units = (int64_t)a.n_rows * a.n_tiles;
+    const bool live = unit < n_units;
+
+    int row = 0, tile = 0;
+    if (live) {
+        tile = (int)(unit / a.n_rows);
+        const int p = (int)(unit - (int64_t)tile * a.n_rows);
+        row = a.order ? a.order[p] : p;
+    }
+    const int col = tile * (G * VEC) + lig * VEC;
+    const bool col_ok = live && col < a.d;
+    const float* xcol = a.x + (col_ok ? col : 0);  // idle lanes read (and discard) column 0
+
+    Slice<VEC> total;
+    total.zero();
+
+    for (int k = 0; k < (DDS ? a.parts : 1); ++k) {
+        int start = 0, len = 0;
+        if (live) {
+            const int32_t* p = a.pos + (int64_t)k * ((int64_t)a.n_rows + 1) + row;
+            start = p[0];
+            len = p[1] - start;
+        }
+        const int64_t col_base = DDS ? (int64_t)k * a.cols_per_part : 0;
+        Slice<VEC> acc;
+        acc.zero();
+
+        // every lane of the warp runs the same number of batches
+        const int max_len = __reduce_max_sync(0xffffffffu, len);
+        int my_c = -1;
+        float my_v = 0.f;
+        if (lig < len) {
+            my_c = a.idx[start + lig];
+            my_v = a.vals[start + lig];
+        }
+        for (int base = 0; base < max_len; base += G) {
+            // next batch of indices / values, one iteration ahead of its use
+            int nx_c = -1;
+            float nx_v = 0.f;
+            if (base + G + lig < len) {
+                nx_c = a.idx[start + base + G + lig];
+                nx_v = a.vals[start + base + G + lig];
+            }
+#pragma unroll
+            for (int j0 = 0; j0 < G; j0 += CH) {
+                if (base + j0 >= max_len) break;  // warp-uniform
+                int c[CH];
+                float v[CH];
+                Slice<VEC> xr[CH];
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    c[j] = __shfl_sync(0xffffffffu, my_c, j0 + j, G);
+                    v[j] = __shfl_sync(0xffffffffu, my_v, j0 + j, G);
+                }
+                // Unconditional loads (padding slots re-read row 0 of the slice) so that all
+                // CH gathers are in flight before the first dependent add.
+#pragma unroll
+                for (int j = 0; j < CH; ++j)
+                    xr[j].load(xcol + (col_base + (c[j] < 0 ? 0 : c[j])) * a.d);
+                // Branch-free commit: a branch here would let the compiler sink each load
+                // next to its use and serialise the gathers.
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    Slice<VEC> next = acc;
+                    next.axpy(v[j], xr[j]);
+                    acc.select(c[j] >= 0, next);
+                }
+            }
+            my_c = nx_c;
+            my_v = nx_v;
+        }
+        if (DDS)
+            total.add(acc);
+        else
+            total = acc;
+    }
+    if (col_ok) total.store(a.out + (int64_t)row * a.d + col);
+}
+
+template <int G, int VEC>
+int launch(const SpmmArgs& a, bool dds, cudaStream_t s) {
+    const int64_t n_units = (int64_t)a.n_rows * a.n_tiles;
+    const int64_t units_per_block = kThreads / G;
+    const int64_t blocks = (n_units + units_per_block - 1) / units_per_block;
+    if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
+    if (blocks == 0) return FG_OK;
+    if (dds)
+        spmm_rows_kernel<G, VEC, true><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+    else
+        spmm_rows_kernel<G, VEC, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+    FG_CUDA_TRY(cudaGetLastError());
+    return FG_OK;
+}
+
+// Feature-tile width (floats) when the caller leaves the choice to the library: the widest
+// power of two, at most 128, whose gathered slice of x (n_cols rows of tile*4 bytes) fits the
+// share of L2 that stays resident under all-SM random access; never below 32 floats, one full
+// 128-byte line per gather.  If not even a 32-float slice fits, residency is out of reach and
+// the widest tile wins (fewest passes over the index arrays, longest contiguous gathers).
+int auto_tile(int64_t n_cols, int d) {
+    static thread_local int64_t l2_bytes = -1;
+    if (l2_bytes < 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) == cudaSuccess)
+            l2_bytes = v;
+        else
+            l2_bytes = 64ll << 20;
+    }
+    const int64_t budget = l2_bytes / 2;  // each half of the chip caches its own copy
+    const int cap = fg::pow2_ceil(d < 128 ? d : 128);
+    if (n_cols * 32 * 4 > budget) return cap;
+    int tile = 32;
+    while (tile * 2 <= cap && n_cols * (int64_t)(tile * 2) * 4 <= budget) tile *= 2;
+    return tile < cap ? tile : cap;
+}
+
+int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int32_t* idx,
+                  const float* vals, const float* x, float* out, int64_t n_rows, int64_t n_cols,
+                  int64_t nnz, int32_t d, int32_t parts, int32_t feat_tile, void* stream,
+                  bool dds) {
+    if (n_rows < 0 || n_cols < 0 || nnz < 0 || d < 1)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d",
+                        (long long)n_rows, (long long)n_cols, (long long)nnz, d);
+    if (n_rows > INT32_MAX || n_cols > INT32_MAX || nnz > INT32_MAX)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "sizes beyond int32 indexing are not supported");
+    if (parts < 1) return fg::fail(FG_ERR_INVALID_ARGUMENT, "num_col_partitions must be >= 1");
+    if (feat_tile != 0 && (feat_tile < 4 || feat_tile > 128 || (feat_tile & (feat_tile - 1))))
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "feat_tile=%d: want 0 or a power of two in 4..128",
+                        feat_tile);
+    if (n_rows == 0) return FG_OK;
+    if (!pos || !out) return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL position or output array");
+    if (nnz > 0 && (!idx || !vals || !x))
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL adjacency or feature array");
+    if (schedule && fg_row_schedule_num_rows(schedule) != n_rows)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row schedule was built for %lld rows, not %lld",
+                        (long long)fg_row_schedule_num_rows(schedule), (long long)n_rows);
+
+    SpmmArgs a;
+    a.pos = pos;
+    a.idx = idx;
+    a.vals = vals;
+    a.x = x;
+    a.out = out;
+    a.order = schedule ? fg_row_schedule_order(schedule) : nullptr;
+    a.n_rows = (int32_t)n_rows;
+    a.d = d;
+    a.parts = parts;
+    a.cols_per_part = dds ? (int32_t)((n_cols + parts - 1) / parts) : 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    const bool vec = (d % 4 == 0) && fg::aligned16(x) && fg::aligned16(out);
+    if (!vec) {
+        // scalar path: 32 lanes x 1 float per unit
+        a.n_tiles = (d + 31) / 32;
+        return launch<32, 1>(a, dds, s);
+    }
+    int tile = feat_tile ? feat_tile : auto_tile(n_cols, d);
+    const int cap = fg::pow2_ceil(d);
+    if (tile > cap) tile = cap;
+    if (tile < 4) tile = 4;
+    a.n_tiles = (d + tile - 1) / tile;
+    switch (tile / 4) {
+        case 1: return launch<1, 4>(a, dds, s);
+        case 2: return launch<2, 4>(a, dds, s);
+        case 4: return launch<4, 4>(a, dds, s);
+        case 8: return launch<8, 4>(a, dds, s);
+        case 16: return launch<16, 4>(a, dds, s);
+        default: return launch<32, 4>(a, dds, s);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int fg_spmm_csr_f32(const fg_row_schedule* schedule, const int32_t* d_indptr,
+                    const int32_t* d_indices, const float* d_vals, const float* d_x, float* d_out,
+                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d, int32_t feat_tile,
+                    void* stream) {
+    return spmm_dispatch(schedule, d_indptr, d_indices, d_vals, d_x, d_out, n_rows, n_cols, nnz, d,
+                         1, feat_tile, stream, false);
+}
+
+int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
+                    const int32_t* d_s1_idx, const float* d_vals, const float* d_x, float* d_out,
+                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                    int32_t num_col_partitions, int32_t feat_tile, void* stream) {
+    return spmm_dispatch(schedule, d_s1_pos, d_s1_idx, d_vals, d_x, d_out, n_rows, n_cols, nnz, d,
+                         num_col_partitions, feat_tile, stream, true);
+}
+
+}  // extern "C"

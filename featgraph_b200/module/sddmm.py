@@ -1,0 +1,196 @@
+"""SDDMM modules: same lifecycle and names as python/featgraph/module/sddmm.py of the
+reference, executed by hand-written sm_100a kernels through the C ABI.
+
+Both classes run on the GPU.  ``VanillaSDDMMx86`` keeps the x86 class's 2-D partitioning
+knobs (the edge list is regrouped tile by tile and ``edge_mapping`` undoes it);
+``VanillaSDDMMcuda`` takes the edge list as given.
+"""
+import numpy as np
+import torch
+
+from ..placeholder import check_float32, static_shape
+from ..util import util_partition_adj_coo_2d
+from . import _device as dev
+
+
+class SDDMMbase:
+    """Counterpart of ``SDDMMbase`` (python/featgraph/module/sddmm.py:11-165)."""
+
+    _compute_keys = ()
+    _schedule_keys = ()
+
+    def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device=None):
+        # COO in SDDMM-like kernels (reference :28-31)
+        adj_coo = adj_scipy.tocoo() if adj_scipy.format != "coo" else adj_scipy
+        self._num_rows, self._num_cols = adj_coo.shape
+        assert num_row_partitions >= 1, "num_row_partitions should be larger than or equal to 1"
+        assert num_col_partitions >= 1, "num_col_partitions should be larger than or equal to 1"
+        self._num_row_partitions = int(num_row_partitions)
+        # Kept from the reference (:37): the column-partition count is taken from the ROW
+        # argument, so the tiling is always square in partition counts.
+        self._num_col_partitions = int(num_row_partitions)
+        self._target = None
+        self._register()
+        self._device = dev.resolve_device(device)
+        if self._num_row_partitions > 1 or self._num_col_partitions > 1:
+            edge_ids, rows, cols = util_partition_adj_coo_2d(
+                adj_coo, self._num_row_partitions, self._num_col_partitions)
+            self._edge_mapping = np.argsort(edge_ids)
+        else:
+            rows, cols = adj_coo.row, adj_coo.col
+        if rows.dtype != np.int32 or cols.dtype != np.int32:
+            raise TypeError("int32 COO index arrays are required (got %s / %s)" % (rows.dtype, cols.dtype))
+        self._nnz = int(rows.shape[0])
+        import ctypes
+        with torch.cuda.device(self._device):
+            self._adj_row = dev.upload(rows, self._device)
+            self._adj_col = dev.upload(cols, self._device)
+            sorted_flag = ctypes.c_int32(0)
+            dev.check(dev.lib().fg_coo_validate(dev.ptr(self._adj_row), dev.ptr(self._adj_col),
+                                                self._num_rows, self._num_cols, self._nnz,
+                                                ctypes.byref(sorted_flag),
+                                                dev.stream_ptr(self._device)))
+        self._rows_sorted = int(sorted_flag.value)
+        self._shapes = None
+        self.out = None
+
+    def _register(self):
+        raise NotImplementedError("Please register target.")
+
+    def _plan(self, input_placeholders, compute_args, schedule_args):
+        compute_args = dict(compute_args or {})
+        schedule_args = dict(schedule_args or {})
+        for k in compute_args:
+            if k not in self._compute_keys:
+                raise TypeError("unexpected compute argument %r" % (k,))
+        for k in schedule_args:
+            if k not in self._schedule_keys:
+                raise TypeError("unexpected schedule argument %r" % (k,))
+        if len(input_placeholders) != 2:
+            raise TypeError("SDDMM takes two inputs (column-side and row-side features)")
+        src_shape = static_shape(input_placeholders[0])
+        dst_shape = static_shape(input_placeholders[1])
+        check_float32(input_placeholders[0])
+        check_float32(input_placeholders[1])
+        if len(src_shape) != 2 or len(dst_shape) != 2:
+            raise ValueError("feature matrices must be 2-D")
+        assert dst_shape[1] == src_shape[1], "dimension mismatch"
+        # The first matrix is gathered by COLUMN id, the second by ROW id
+        # (python/featgraph/op/vanilla_sddmm.py:47; tests/test_module_sddmm.py:18-19).
+        if src_shape[0] != self._num_cols or dst_shape[0] != self._num_rows:
+            raise ValueError("expected shapes [%d, d] and [%d, d], got %s and %s"
+                             % (self._num_cols, self._num_rows, src_shape, dst_shape))
+        d = src_shape[1]
+        nfp = int(compute_args.get("num_feat_partitions", schedule_args.get("num_feat_partitions", 1)))
+        if nfp < 1 or d % nfp != 0:
+            raise ValueError("feat_len %d is not divisible by num_feat_partitions %d" % (d, nfp))
+        self._check_schedule(schedule_args, nfp)
+        return src_shape, dst_shape, d, nfp
+
+    def _check_schedule(self, schedule_args, nfp):
+        pass
+
+    def build(self, input_placeholders, compute_args, schedule_args):
+        """Fix the feature shapes and allocate the (reused) per-edge output (reference :72-92)."""
+        src_shape, dst_shape, _, _ = self._plan(input_placeholders, compute_args, schedule_args)
+        self._shapes = (src_shape, dst_shape)
+        self.out = torch.zeros((self._nnz,), dtype=torch.float32, device=self._device)
+
+    def lower_to_ir(self, input_placeholders, compute_args, schedule_args):
+        """Text description of what ``build`` + ``run`` would launch (reference :94-113)."""
+        _, _, d, nfp = self._plan(input_placeholders, compute_args, schedule_args)
+        return ("featgraph_b200 sddmm: rows=%d cols=%d nnz=%d feat_len=%d num_feat_partitions=%d "
+                "edge_order=%s rows_sorted=%d kernel=fg_sddmm_coo_f32 device=%s"
+                % (self._num_rows, self._num_cols, self._nnz, d, nfp,
+                   "2d(%dx%d)" % (self._num_row_partitions, self._num_col_partitions)
+                   if self._num_row_partitions > 1 else "as_given", self._rows_sorted, self._device))
+
+    def _launch(self, src, dst, out):
+        d = self._shapes[0][1]
+        dev.check(dev.lib().fg_sddmm_coo_f32(dev.ptr(self._adj_row), dev.ptr(self._adj_col),
+                                             dev.ptr(src), dev.ptr(dst), dev.ptr(out),
+                                             self._num_rows, self._num_cols, self._nnz, d,
+                                             self._rows_sorted, dev.stream_ptr(self._device)))
+
+    def run(self, inputs):
+        """Enqueue the kernel on the current stream; returns the module's output tensor (the
+        same object every call, reference :115-129).  Argument order: [column-side, row-side]."""
+        if self.out is None:
+            raise RuntimeError("call build() before run()")
+        src, dst = inputs
+        dev.check_input(src, self._shapes[0], self._device, "column-side features")
+        dev.check_input(dst, self._shapes[1], self._device, "row-side features")
+        with torch.cuda.device(self._device):
+            self._launch(src, dst, self.out)
+        return self.out
+
+    def run_host(self, inputs, out=None):
+        """Host-buffer call: features host->device, kernel, result device->host, wait."""
+        ts = [torch.from_numpy(x) if isinstance(x, np.ndarray) else x for x in inputs]
+        with torch.cuda.device(self._device):
+            ds = [t.to(self._device, non_blocking=True) for t in ts]
+            res = self.run(ds)
+            if out is None:
+                return res.cpu()
+            out.copy_(res, non_blocking=True)
+            torch.cuda.current_stream(self._device).synchronize()
+            return out
+
+    def measure_average_time(self, inputs, num_runs):
+        """Mean seconds per call over ``num_runs`` back-to-back calls (reference :131-150)."""
+        self.run(inputs)
+        return dev.time_calls(lambda: self._launch(inputs[0], inputs[1], self.out), self._device,
+                              num_runs)
+
+    @property
+    def edge_mapping(self):
+        """Permutation that puts the output back into the caller's edge order:
+        ``out[edge_mapping]`` (reference :152-157)."""
+        assert self._target != 'cuda', "no graph partitioning on cuda, no edge_mapping"
+        assert self._num_row_partitions > 1 or self._num_col_partitions > 1, \
+            "no graph partitioning, no edge_mapping"
+        return self._edge_mapping
+
+    @property
+    def ctx(self):
+        return self._device
+
+    @property
+    def target(self):
+        return self._target
+
+
+class VanillaSDDMMx86(SDDMMbase):
+    """The x86 class of the reference (python/featgraph/module/sddmm.py:168-176)."""
+
+    _compute_keys = ("num_feat_partitions",)
+    _schedule_keys = ("num_feat_partitions",)
+
+    def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device=None):
+        super().__init__(adj_scipy, num_row_partitions, num_col_partitions, device)
+
+    def _register(self):
+        self._target = "llvm"
+
+
+class VanillaSDDMMcuda(SDDMMbase):
+    """The CUDA class of the reference (python/featgraph/module/sddmm.py:179-187).
+    ``num_cuda_blocks`` is checked as the reference's schedule checks it
+    (python/featgraph/op/vanilla_sddmm.py:79-82) and otherwise has no effect."""
+
+    _compute_keys = ()
+    _schedule_keys = ("num_feat_partitions", "num_cuda_blocks")
+
+    def __init__(self, adj_scipy, device=None):
+        super().__init__(adj_scipy, 1, 1, device)
+
+    def _register(self):
+        self._target = "cuda"
+
+    def _check_schedule(self, schedule_args, nfp):
+        assert nfp == 1, "cuda schedule for sddmm does not support feat dimension tiling, " \
+                         "which requires cross-cuda-block reduction and atomic operations."
+        blocks = schedule_args.get("num_cuda_blocks", 8192)
+        if "num_cuda_blocks" in schedule_args:
+            assert blocks <= self._nnz, "num_cuda_blocks must be smaller than num_edges, " \
+                                        "which is {}.".format(self._nnz)

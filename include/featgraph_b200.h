@@ -1,0 +1,130 @@
+/*
+ * featgraph_b200 - C ABI of the sm_100a SpMM / SDDMM library (libfeatgraph_b200.so).
+ *
+ * What this boundary replaces.  The reference builds each kernel with its code
+ * generator and then calls the resulting packed function with positional array
+ * arguments, destination last:
+ *     SpMM  : func(SrcFeat, indptr, indices, vals, Out)        python/featgraph/module/spmm.py:108-109,159-160
+ *     SpMM  : func(SrcFeat, s1_pos, s1_idx, vals, Out)  (DDS)  python/featgraph/module/spmm.py:100-101,156-157
+ *     SDDMM : func(SrcFeat, DstFeat, row, col, Out)            python/featgraph/module/sddmm.py:89-90,128
+ * The entry points below take the same arrays as plain pointers plus explicit sizes.
+ *
+ * Conventions
+ *  - Every pointer named d_* is a DEVICE pointer on the current CUDA device; h_* is a host
+ *    pointer.  int32 index arrays and fp32 values, as the reference keeps scipy's dtypes
+ *    (module/spmm.py:59-64).  Feature matrices are dense row-major, row stride = d.
+ *  - The caller owns every array.  The library owns only the objects it hands out
+ *    (fg_row_schedule, fg_graph) and frees them in the matching *_destroy call.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Device
+ *    entry points only enqueue work on it; they do not synchronise.
+ *  - Return value: FG_OK or an FG_ERR_* code; fg_last_error() gives the text for the
+ *    calling thread.  Nothing aborts or traps.  Arguments are checked on the host only:
+ *    index arrays are trusted to be in range (fg_csr_validate / fg_coo_validate check them).
+ *  - Arithmetic: fp32, product and sum rounded separately (no fused multiply-add), the model
+ *    of the reference's x86 target (module/spmm.py:202).  SpMM adds a row's nonzeros
+ *    strictly in storage order, so its result does not depend on any launch parameter.
+ *  - Re-entrant; no global mutable state except the thread-local error text.
+ */
+#ifndef FEATGRAPH_B200_H_
+#define FEATGRAPH_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FG_OK 0
+#define FG_ERR_INVALID_ARGUMENT 1
+#define FG_ERR_CUDA 2
+#define FG_ERR_OUT_OF_MEMORY 3
+#define FG_ERR_BAD_INDEX 4
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fg_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). Never NULL. */
+const char* fg_last_error(void);
+
+/* Number of SMs, compute capability and L2 size of the current device.
+ * Replaces the reference's device handle query (tvm.gpu(0), module/spmm.py:218). */
+int fg_device_info(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor, int64_t* l2_bytes);
+
+/* --------------------------------------------------------------------------------------
+ * Row schedule: the order in which SpMM visits rows (heaviest rows first, ties in
+ * row order).  It takes the place of the reference's launch-shape knobs
+ * num_cuda_blocks / num_threads_per_cuda_block (python/featgraph/op/vanilla_spmm.py:128-146),
+ * which only choose how rows map to blocks.  Built once per adjacency on the device;
+ * holds n_rows int32 of device memory.  Results never depend on it.
+ * -------------------------------------------------------------------------------------- */
+typedef struct fg_row_schedule fg_row_schedule;
+
+/* d_indptr: n_rows+1 ascending positions.  Synchronises `stream` before returning. */
+int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream,
+                           fg_row_schedule** out_schedule);
+/* Device pointer to the n_rows row ids in visiting order (valid until destroy). */
+const int32_t* fg_row_schedule_order(const fg_row_schedule* schedule);
+int64_t fg_row_schedule_num_rows(const fg_row_schedule* schedule);
+void fg_row_schedule_destroy(fg_row_schedule* schedule);
+
+/* --------------------------------------------------------------------------------------
+ * SpMM, CSR:  out[r, f] = sum_{e in [indptr[r], indptr[r+1])} vals[e] * x[indices[e], f]
+ * Replaces the function built from vanilla_spmm_csr_x86 / vanilla_spmm_csr_cuda
+ * (python/featgraph/op/vanilla_spmm.py:6-62, 83-125) and called at module/spmm.py:159-160.
+ *   schedule   NULL = visit rows in index order.
+ *   feat_tile  width in floats of the feature slice handled per pass over the rows
+ *              (power of two, 4..128), 0 = choose from n_cols and the L2 size.  It is the
+ *              reference's num_feat_partitions idea (op/vanilla_spmm.py:41-44) used to keep
+ *              the gathered slice of x resident in L2.  No effect on the values.
+ * x: [n_cols, d], out: [n_rows, d].  Any d >= 1; 128-bit gathers need d % 4 == 0 and
+ * 16-byte aligned x / out, otherwise a scalar kernel runs.
+ * -------------------------------------------------------------------------------------- */
+int fg_spmm_csr_f32(const fg_row_schedule* schedule, const int32_t* d_indptr,
+                    const int32_t* d_indices, const float* d_vals, const float* d_x, float* d_out,
+                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d, int32_t feat_tile,
+                    void* stream);
+
+/* SpMM, DDS (column-partitioned CSR made by util_convert_csr_to_dds,
+ * python/featgraph/util/adj_partitioning.py:7-57):
+ *   out[r, f] = sum_{k < num_col_partitions} ( sum_{e in segment(k, r)} vals[e] * x[s1_idx[e] + k*w, f] )
+ * with w = ceil(n_cols / num_col_partitions) and segment(k, r) =
+ * [s1_pos[k*(n_rows+1) + r], s1_pos[k*(n_rows+1) + r + 1]).  Inner sums start at 0 and run in
+ * storage order, the outer sum starts at 0 and adds partitions in ascending k: the
+ * association of vanilla_spmm_dds_x86 (op/vanilla_spmm.py:195-218), called at
+ * module/spmm.py:156-157. */
+int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
+                    const int32_t* d_s1_idx, const float* d_vals, const float* d_x, float* d_out,
+                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                    int32_t num_col_partitions, int32_t feat_tile, void* stream);
+
+/* --------------------------------------------------------------------------------------
+ * SDDMM, COO:  out[e] = sum_k src[col[e], k] * dst[row[e], k]
+ * (src is indexed by the COLUMN id, dst by the ROW id: python/featgraph/op/vanilla_sddmm.py:47).
+ * Replaces the function built from vanilla_sddmm (op/vanilla_sddmm.py:6-63) and called at
+ * module/sddmm.py:128.  Edges may come in any order; out keeps that order.
+ *   rows_sorted  non-zero promises that d_row is non-decreasing (a CSR-ordered edge list):
+ *                the row-side feature row is then kept in registers across a row's edges.
+ *                Zero is always safe.
+ * src: [n_cols, d], dst: [n_rows, d], out: [nnz].  The dot product is summed as a fixed
+ * tree (per-lane partial sums, then a butterfly), not in ascending k; the difference from
+ * the sequential sum is bounded by fp32 rounding of d terms.
+ * -------------------------------------------------------------------------------------- */
+int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src,
+                     const float* d_dst, float* d_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                     int32_t d, int32_t rows_sorted, void* stream);
+
+/* --------------------------------------------------------------------------------------
+ * Index checks (the code generator of the reference emits shape asserts only; these add
+ * the range checks that keep a bad adjacency from reading out of bounds).  Both
+ * synchronise `stream` and return FG_ERR_BAD_INDEX with a message naming the first kind
+ * of violation found.  *rows_sorted (may be NULL) reports whether d_row is non-decreasing.
+ * -------------------------------------------------------------------------------------- */
+int fg_csr_validate(const int32_t* d_indptr, const int32_t* d_indices, int64_t n_rows,
+                    int64_t n_cols, int64_t nnz, void* stream);
+int fg_coo_validate(const int32_t* d_row, const int32_t* d_col, int64_t n_rows, int64_t n_cols,
+                    int64_t nnz, int32_t* rows_sorted, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FEATGRAPH_B200_H_ */

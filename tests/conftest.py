@@ -1,0 +1,49 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+# Tolerance the hot path is held to against the CPU oracle for floating point
+# (SDDMM; SpMM is compared bit for bit).
+RTOL = 1e-5
+ATOL = 1e-4
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def numeric_golden():
+    return dict(np.load(os.path.join(GOLDEN, "numeric_cases.npz")))
+
+
+@pytest.fixture(scope="session")
+def partition_golden():
+    return dict(np.load(os.path.join(GOLDEN, "partition_cases.npz")))
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    import oracle as _oracle
+    _oracle.lib()
+    return _oracle
+
+
+def reference_util_or_skip():
+    """The reference's own partitioners, loaded by file path, or skip where the checkout is absent."""
+    import importlib.util
+    path = "/root/reference/python/featgraph/util/adj_partitioning.py"
+    if not os.path.exists(path):
+        pytest.skip("reference checkout not present on this machine")
+    spec = importlib.util.spec_from_file_location("reference_adj_partitioning", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod

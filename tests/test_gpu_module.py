@@ -1,0 +1,143 @@
+"""The module layer on the GPU, written the way the reference's own tests are
+(tests/test_module_spmm.py, tests/test_module_sddmm.py): same matrix shape, feature length,
+knob tuples and scipy / numpy ground truth, plus the oracle."""
+import numpy as np
+import pytest
+import scipy.sparse as sp
+import torch
+
+from conftest import ATOL, RTOL
+from featgraph import placeholder
+from featgraph.module import VanillaSDDMMcuda, VanillaSDDMMx86, VanillaSpMMcuda, VanillaSpMMx86
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def adj_csr():
+    return sp.random(127, 255, density=0.1, format="csr", random_state=42).astype("float32")
+
+
+@pytest.fixture(scope="module")
+def adj_coo():
+    return sp.random(127, 255, density=0.1, format="coo", random_state=43).astype("int32")
+
+
+@pytest.mark.parametrize("feat_len,num_col_partitions,num_feat_partitions", [(128, 1, 1), (128, 4, 1), (128, 4, 4)])
+def test_vanilla_spmm_x86(oracle, adj_csr, feat_len, num_col_partitions, num_feat_partitions):
+    num_rows, num_cols = adj_csr.shape
+    module = VanillaSpMMx86(adj_csr, num_col_partitions)
+    SrcFeat = placeholder((num_cols, feat_len))
+    module.build([SrcFeat], {'num_feat_partitions': num_feat_partitions}, {})
+    src_feat_np = np.random.default_rng(0).random((num_cols, feat_len), dtype=np.float32)
+    out = module.run([torch.from_numpy(src_feat_np).to(module.ctx)]).cpu().numpy()
+    np.testing.assert_allclose(adj_csr.dot(src_feat_np), out, rtol=1e-4, atol=1e-4)
+    if num_col_partitions == 1:
+        want = oracle.spmm_csr(adj_csr.indptr, adj_csr.indices, adj_csr.data, src_feat_np,
+                               num_feat_partitions=num_feat_partitions)
+    else:
+        from featgraph.util import util_convert_csr_to_dds
+        want = oracle.spmm_dds(*util_convert_csr_to_dds(adj_csr, num_col_partitions), src_feat_np, num_rows,
+                               num_col_partitions, num_feat_partitions=num_feat_partitions)
+    np.testing.assert_array_equal(out, want)
+    assert module.target == 'llvm'
+
+
+@pytest.mark.parametrize("num_threads_per_cuda_block", [32, 128, None])
+def test_vanilla_spmm_cuda(oracle, adj_csr, num_threads_per_cuda_block):
+    num_rows, num_cols = adj_csr.shape
+    module = VanillaSpMMcuda(adj_csr)
+    SrcFeat = placeholder((num_cols, 128))
+    module.build([SrcFeat], {}, {'num_threads_per_cuda_block': num_threads_per_cuda_block})
+    src_feat_np = np.random.default_rng(1).random((num_cols, 128), dtype=np.float32)
+    out_t = module.run([torch.from_numpy(src_feat_np).to(module.ctx)])
+    out = out_t.cpu().numpy()
+    np.testing.assert_allclose(adj_csr.dot(src_feat_np), out, rtol=1e-4, atol=1e-4)
+    np.testing.assert_array_equal(out, oracle.spmm_csr(adj_csr.indptr, adj_csr.indices, adj_csr.data, src_feat_np))
+    # destination passing: the same tensor comes back on every run
+    assert module.run([torch.from_numpy(src_feat_np).to(module.ctx)]) is out_t
+    assert module.target == 'cuda' and module.ctx.type == 'cuda'
+    assert module.measure_average_time([torch.from_numpy(src_feat_np).to(module.ctx)], 3) > 0
+    assert "fg_spmm_csr_f32" in module.lower_to_ir([SrcFeat], {}, {})
+
+
+def test_spmm_accepts_coo_input_and_run_host(adj_csr):
+    module = VanillaSpMMcuda(adj_csr.tocoo())
+    module.build([placeholder((255, 64))], {}, {})
+    x = np.random.default_rng(2).random((255, 64), dtype=np.float32)
+    out = module.run_host([x])
+    np.testing.assert_allclose(adj_csr.dot(x), out.numpy(), rtol=1e-4, atol=1e-4)
+
+
+def test_spmm_build_and_run_argument_errors(adj_csr):
+    module = VanillaSpMMcuda(adj_csr)
+    with pytest.raises(TypeError):
+        module.build([placeholder((255, 64))], {'num_feat_partitions': 2}, {})  # not a cuda compute arg
+    with pytest.raises(ValueError):
+        module.build([placeholder((254, 64))], {}, {})
+    with pytest.raises(RuntimeError):
+        module.run([torch.zeros(255, 64, device=module.ctx)])
+    module.build([placeholder((255, 64))], {}, {})
+    with pytest.raises(ValueError):
+        module.run([torch.zeros(255, 32, device=module.ctx)])
+    with pytest.raises(TypeError):
+        module.run([torch.zeros(255, 64, device=module.ctx, dtype=torch.float64)])
+    with pytest.raises(ValueError):
+        VanillaSpMMx86(adj_csr, 2).build([placeholder((255, 30))], {'num_feat_partitions': 4}, {})
+    with pytest.raises(AssertionError):
+        VanillaSpMMx86(adj_csr, 0)
+
+
+@pytest.mark.parametrize("feat_len,num_feat_partitions,num_row_partitions,num_col_partitions",
+                         [(128, 1, 1, 1), (128, 4, 1, 1), (128, 4, 4, 4)])
+def test_vanilla_sddmm_x86(oracle, adj_coo, feat_len, num_feat_partitions, num_row_partitions, num_col_partitions):
+    adj = adj_coo.copy()
+    num_rows, num_cols = adj.shape
+    module = VanillaSDDMMx86(adj, num_row_partitions, num_col_partitions)
+    SrcFeat = placeholder((num_cols, feat_len))
+    DstFeat = placeholder((num_rows, feat_len))
+    module.build([SrcFeat, DstFeat], {'num_feat_partitions': num_feat_partitions},
+                 {'num_feat_partitions': num_feat_partitions})
+    rng = np.random.default_rng(3)
+    src_feat_np = rng.random((num_cols, feat_len), dtype=np.float32)
+    dst_feat_np = rng.random((num_rows, feat_len), dtype=np.float32)
+    out = module.run([torch.from_numpy(src_feat_np).to(module.ctx),
+                      torch.from_numpy(dst_feat_np).to(module.ctx)]).cpu().numpy()
+    if num_row_partitions != 1 or num_col_partitions != 1:
+        out = out[module.edge_mapping]
+    out_numpy = (src_feat_np[adj.col] * dst_feat_np[adj.row]).sum(axis=-1)
+    np.testing.assert_allclose(out_numpy, out, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(out, oracle.sddmm(adj.row, adj.col, src_feat_np, dst_feat_np,
+                                                 num_feat_partitions=num_feat_partitions), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("num_cuda_blocks", [32, 256])
+def test_vanilla_sddmm_cuda(oracle, adj_coo, num_cuda_blocks):
+    num_rows, num_cols = adj_coo.shape
+    module = VanillaSDDMMcuda(adj_coo)
+    SrcFeat = placeholder((num_cols, 128))
+    DstFeat = placeholder((num_rows, 128))
+    module.build([SrcFeat, DstFeat], {}, {'num_cuda_blocks': num_cuda_blocks})
+    rng = np.random.default_rng(4)
+    src_feat_np = rng.random((num_cols, 128), dtype=np.float32)
+    dst_feat_np = rng.random((num_rows, 128), dtype=np.float32)
+    ins = [torch.from_numpy(src_feat_np).to(module.ctx), torch.from_numpy(dst_feat_np).to(module.ctx)]
+    out = module.run(ins).cpu().numpy()
+    out_numpy = (src_feat_np[adj_coo.col] * dst_feat_np[adj_coo.row]).sum(axis=-1)
+    np.testing.assert_allclose(out_numpy, out, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(out, oracle.sddmm(adj_coo.row, adj_coo.col, src_feat_np, dst_feat_np),
+                               rtol=RTOL, atol=ATOL)
+    assert module.measure_average_time(ins, 3) > 0
+    with pytest.raises(AssertionError):
+        module.edge_mapping  # no partitioning on cuda
+    with pytest.raises(AssertionError):
+        module.build([SrcFeat, DstFeat], {}, {'num_cuda_blocks': adj_coo.nnz + 1})
+
+
+def test_sddmm_quirk_column_partitions_follow_row_argument(adj_coo):
+    """python/featgraph/module/sddmm.py:37: num_col_partitions is overwritten by num_row_partitions."""
+    m = VanillaSDDMMx86(adj_coo.copy(), 1, 4)
+    with pytest.raises(AssertionError):
+        m.edge_mapping  # 1 x 1 after the overwrite: not partitioned
+    m = VanillaSDDMMx86(adj_coo.copy(), 3, 1)
+    assert m.edge_mapping.shape == (adj_coo.nnz,) and m.edge_mapping.dtype == np.int64

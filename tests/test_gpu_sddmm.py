@@ -1,0 +1,108 @@
+"""SDDMM on the GPU, through the C ABI, against the CPU oracle, within rtol 1e-5 / atol 1e-4
+(the kernel sums a dot product as a tree, the oracle in ascending k)."""
+import numpy as np
+import pytest
+import scipy.sparse as sp
+
+from conftest import ATOL, RTOL
+
+pytestmark = pytest.mark.gpu
+
+
+def _feat(m, d, seed):
+    return (np.random.default_rng(seed).random((m, d), dtype=np.float32) * 2 - 1).astype(np.float32)
+
+
+def test_reference_test_shape_fixture(oracle, numeric_golden):
+    import gpu_util as G
+    g = numeric_golden
+    out = G.sddmm(g["coo_row"], g["coo_col"], g["x"], g["y"])
+    np.testing.assert_allclose(out, oracle.sddmm(g["coo_row"], g["coo_col"], g["x"], g["y"]), rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(g["sddmm_numpy"], out, rtol=1e-4, atol=1e-4)  # the reference's own check
+
+
+@pytest.mark.parametrize("d", [1, 3, 4, 8, 20, 32, 33, 48, 64, 100, 128, 200, 256, 384, 512, 640])
+@pytest.mark.parametrize("order", ["csr", "shuffled"])
+def test_feature_lengths_and_edge_orders(oracle, d, order):
+    import gpu_util as G
+    coo = sp.random(127, 255, density=0.1, format="csr", random_state=d).tocoo()
+    row, col = coo.row.astype(np.int32), coo.col.astype(np.int32)
+    if order == "shuffled":
+        perm = np.random.default_rng(d).permutation(len(row))
+        row, col = row[perm], col[perm]
+    src, dst = _feat(255, d, 1), _feat(127, d, 2)
+    want = oracle.sddmm(row, col, src, dst)
+    np.testing.assert_allclose(G.sddmm(row, col, src, dst, rows_sorted=0), want, rtol=RTOL, atol=ATOL)
+    if order == "csr":
+        np.testing.assert_allclose(G.sddmm(row, col, src, dst, rows_sorted=1), want, rtol=RTOL, atol=ATOL)
+
+
+def test_exact_on_small_integers():
+    """Integer-valued features make every fp32 operation exact, whatever the summation tree."""
+    import gpu_util as G
+    rng = np.random.default_rng(4)
+    coo = sp.random(90, 70, density=0.2, format="csr", random_state=4).tocoo()
+    for d in (32, 128, 512):
+        src = rng.integers(-8, 9, size=(70, d)).astype(np.float32)
+        dst = rng.integers(-8, 9, size=(90, d)).astype(np.float32)
+        want = (src.astype(np.int64)[coo.col] * dst.astype(np.int64)[coo.row]).sum(-1).astype(np.float32)
+        for s in (0, 1):
+            np.testing.assert_array_equal(G.sddmm(coo.row, coo.col, src, dst, rows_sorted=s), want)
+
+
+def test_ragged_edge_counts_and_empty(oracle):
+    import gpu_util as G
+    src, dst = _feat(40, 64, 1), _feat(30, 64, 2)
+    rng = np.random.default_rng(0)
+    for nnz in (0, 1, 31, 32, 33, 255, 256, 257, 2049):
+        row = np.sort(rng.integers(0, 30, size=nnz)).astype(np.int32)
+        col = rng.integers(0, 40, size=nnz).astype(np.int32)
+        out = G.sddmm(row, col, src, dst, rows_sorted=1)
+        assert out.shape == (nnz,)
+        np.testing.assert_allclose(out, oracle.sddmm(row, col, src, dst), rtol=RTOL, atol=ATOL)
+
+
+def test_long_rows_in_csr_order(oracle):
+    import gpu_util as G
+    from featgraph_b200 import graphgen
+    deg = np.full(20, 3, dtype=np.int64)
+    deg[7] = 20000
+    a = graphgen._csr_from_degrees(deg, 25000, seed=5).tocoo()
+    src = graphgen.uniform_features((25000, 128), seed=6)
+    dst = graphgen.uniform_features((20, 128), seed=7)
+    np.testing.assert_allclose(G.sddmm(a.row, a.col, src, dst, rows_sorted=1),
+                               oracle.sddmm(a.row, a.col, src, dst), rtol=RTOL, atol=ATOL)
+
+
+def test_2d_partition_order_and_edge_mapping(oracle, numeric_golden):
+    import gpu_util as G
+    from featgraph_b200.util import util_partition_adj_coo_2d
+    g = numeric_golden
+    coo = sp.coo_matrix((np.ones(len(g["coo_row"]), np.int32), (g["coo_row"], g["coo_col"])), shape=(127, 255))
+    ids, r, c = util_partition_adj_coo_2d(coo, 4, 4)
+    out = G.sddmm(r, c, g["x"], g["y"])[np.argsort(ids)]
+    np.testing.assert_allclose(out, oracle.sddmm(g["coo_row"], g["coo_col"], g["x"], g["y"]), rtol=RTOL, atol=ATOL)
+
+
+def test_workload_c1_full_size(oracle):
+    """100,000 nodes, 32 neighbours per row, d = 128: 3.2 M edges."""
+    import gpu_util as G
+    from featgraph_b200 import graphgen
+    a = graphgen.workload_graph("C1").tocoo()
+    src = graphgen.workload_features("C1", 100_000, 128, 0)
+    dst = graphgen.workload_features("C1", 100_000, 128, 1)
+    want = oracle.sddmm(a.row, a.col, src, dst, threads=8)
+    np.testing.assert_allclose(G.sddmm(a.row, a.col, src, dst, rows_sorted=1), want, rtol=RTOL, atol=ATOL)
+
+
+def test_coo_validate_reports_order_and_range():
+    import ctypes
+    import gpu_util as G
+    from featgraph_b200 import _native
+    L = _native.lib()
+    flag = ctypes.c_int32(-1)
+    r, c = G.dev(np.array([0, 0, 1, 2], np.int32)), G.dev(np.array([3, 1, 0, 2], np.int32))
+    assert L.fg_coo_validate(G.p(r), G.p(c), 3, 4, 4, ctypes.byref(flag), G.stream()) == 0 and flag.value == 1
+    r2 = G.dev(np.array([0, 2, 1, 2], np.int32))
+    assert L.fg_coo_validate(G.p(r2), G.p(c), 3, 4, 4, ctypes.byref(flag), G.stream()) == 0 and flag.value == 0
+    assert L.fg_coo_validate(G.p(r2), G.p(c), 2, 4, 4, ctypes.byref(flag), G.stream()) == 4
