@@ -58,11 +58,11 @@ class _DeviceInt32View:
 
     def __init__(self, address, count):
         self.__cuda_array_interface__ = {
-            "shape": (int(count),), "typestr": "<i4", "data": (int(address), True), "version": 2}
+            "shape": (int(count),), "typestr": "<i4", "data": (int(address), False), "version": 2}
 
 
 def view_device_int32(address, count, device):
-    """Read-only torch view of ``count`` int32 at a device address owned by the library."""
+    """Torch view (treat as read-only) of ``count`` int32 at a device address owned by the library."""
     return torch.as_tensor(_DeviceInt32View(address, count), device=device)
 
 
