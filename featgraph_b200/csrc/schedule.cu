@@ -9,11 +9,7 @@
 #include <cub/device/device_radix_sort.cuh>
 
 #include "common.cuh"
-
-struct fg_row_schedule {
-    int32_t* d_order = nullptr;
-    int64_t n_rows = 0;
-};
+#include "schedule.cuh"
 
 namespace {
 
@@ -24,6 +20,15 @@ __global__ void degree_keys_kernel(const int32_t* __restrict__ indptr, int64_t n
         keys[r] = (uint32_t)(indptr[r + 1] - indptr[r]);
         rows[r] = (int32_t)r;
     }
+}
+
+// keys are sorted descending: the number of long rows is the position of the last key >= threshold
+__global__ void count_long_rows_kernel(const uint32_t* __restrict__ sorted_keys, int64_t n_rows,
+                                       uint32_t threshold, int32_t* __restrict__ n_long) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows) return;
+    if (sorted_keys[i] >= threshold && (i + 1 == n_rows || sorted_keys[i + 1] < threshold))
+        *n_long = (int32_t)(i + 1);
 }
 
 }  // namespace
@@ -46,6 +51,8 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream
     }
     uint32_t *keys_in = nullptr, *keys_out = nullptr;
     int32_t* rows_in = nullptr;
+    int32_t* d_n_long = nullptr;
+    int32_t h_n_long = 0;
     void* temp = nullptr;
     size_t temp_bytes = 0;
     int rc = FG_OK;
@@ -53,6 +60,7 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream
         cudaFree(keys_in);
         cudaFree(keys_out);
         cudaFree(rows_in);
+        cudaFree(d_n_long);
         cudaFree(temp);
     };
 #define FG_TRY_OR_CLEAN(expr)                                                              \
@@ -82,7 +90,13 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream
     FG_TRY_OR_CLEAN(cudaMalloc(&temp, temp_bytes ? temp_bytes : 1));
     FG_TRY_OR_CLEAN(cub::DeviceRadixSort::SortPairsDescending(
         temp, temp_bytes, keys_in, keys_out, rows_in, sch->d_order, (int)n_rows, 0, 32, s));
+    FG_TRY_OR_CLEAN(cudaMalloc(&d_n_long, sizeof(int32_t)));
+    FG_TRY_OR_CLEAN(cudaMemsetAsync(d_n_long, 0, sizeof(int32_t), s));
+    count_long_rows_kernel<<<blocks, threads, 0, s>>>(keys_out, n_rows, fg::kLongRowThreshold, d_n_long);
+    FG_TRY_OR_CLEAN(cudaGetLastError());
+    FG_TRY_OR_CLEAN(cudaMemcpyAsync(&h_n_long, d_n_long, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
     FG_TRY_OR_CLEAN(cudaStreamSynchronize(s));
+    sch->n_long = h_n_long;
 #undef FG_TRY_OR_CLEAN
     cleanup();
     *out_schedule = sch;
@@ -95,6 +109,10 @@ const int32_t* fg_row_schedule_order(const fg_row_schedule* schedule) {
 
 int64_t fg_row_schedule_num_rows(const fg_row_schedule* schedule) {
     return schedule ? schedule->n_rows : 0;
+}
+
+int64_t fg_row_schedule_num_long_rows(const fg_row_schedule* schedule) {
+    return schedule ? schedule->n_long : 0;
 }
 
 void fg_row_schedule_destroy(fg_row_schedule* schedule) {

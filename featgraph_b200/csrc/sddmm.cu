@@ -3,16 +3,27 @@
 //   out[e] = sum_k src[col[e], k] * dst[row[e], k]      python/featgraph/op/vanilla_sddmm.py:47
 //
 // Work decomposition.  A warp takes 32 consecutive edges at a time: it reads their row and
-// column ids with one coalesced load each, and writes their 32 results with one coalesced
-// store.  In between, groups of G lanes (G*4*NV >= d) each take G consecutive edges of the
-// 32; for one edge the group's lanes gather the d floats of src[col[e]] with 128-bit loads
-// (consecutive lanes, consecutive 16 bytes), multiply by the matching slice of dst[row[e]],
-// add up their own products and finish with a log2(G)-step butterfly of warp shuffles.
-// Several edges' gathers are issued before the first reduction.
+// column ids with one coalesced load each and writes their 32 results with one coalesced
+// store.  In between, groups of G lanes each take G consecutive edges of the 32.  For one
+// edge the group's lanes gather a slice of src[col[e]] with 128-bit loads (consecutive lanes,
+// consecutive 16 bytes) and multiply-accumulate it against the matching slice of dst[row[e]];
+// each lane ends up with G partial sums (one per edge), and a transposed butterfly - G-1
+// shuffles for G edges instead of log2(G) per edge - leaves lane i of the group holding the
+// finished dot product of edge i, which is exactly the layout of the coalesced store.
 //
-// When the edge list is row-sorted (CSR order) the row-side slice stays in registers for
-// as long as consecutive edges share the row, so it is read once per row, not once per
-// edge.  Otherwise both rows are gathered for every edge.
+// Row side.  When the edge list is row-sorted (CSR order) the row-side slice stays in
+// registers while consecutive edges share the row (a ballot marks where rows change), so it is
+// read once per row, not once per edge.  Otherwise both rows are gathered for every edge.
+//
+// Feature tiling.  When the column-side matrix is too large for L2, the feature dimension is
+// cut into tiles whose n_cols x tile slice does fit; one launch per tile, tile t > 0 adding
+// its partial dot product to out[e] (stream order makes the read-modify-write safe).  This is
+// the reference's num_feat_partitions loop order (fo -> edge -> fi, op/vanilla_sddmm.py:70-72)
+// used to keep the gathered slice resident in L2.
+//
+// Arithmetic: fp32 FMA inside a lane, fixed-shape tree across lanes, ascending order across
+// tiles.  Not the sequential k order of the x86 loop; the difference is bounded by fp32
+// rounding of d terms.
 #include "common.cuh"
 
 namespace {
@@ -21,23 +32,35 @@ constexpr int kThreads = 256;
 constexpr int kBatchesPerWarp = 8;  // 8 x 32 consecutive edges per warp
 
 __device__ __forceinline__ float dot4(float acc, const float4& a, const float4& b) {
-    acc = fg::mul_then_add(acc, a.x, b.x);
-    acc = fg::mul_then_add(acc, a.y, b.y);
-    acc = fg::mul_then_add(acc, a.z, b.z);
-    acc = fg::mul_then_add(acc, a.w, b.w);
+    acc = fmaf(a.x, b.x, acc);
+    acc = fmaf(a.y, b.y, acc);
+    acc = fmaf(a.z, b.z, acc);
+    acc = fmaf(a.w, b.w, acc);
     return acc;
 }
 
-// G lanes per edge, NV float4 per lane, U edges in flight per group.
-template <int G, int NV, int U, bool CACHE_DST>
-__global__ void __launch_bounds__(kThreads, 4)
-sddmm_vec4_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ col,
-                  const float* __restrict__ src, const float* __restrict__ dst,
-                  float* __restrict__ out, int64_t nnz, int32_t d) {
+struct SddmmArgs {
+    const int32_t* row;
+    const int32_t* col;
+    const float* src;  // already offset to the tile's first column
+    const float* dst;  // already offset to the tile's first column
+    float* out;
+    int64_t nnz;
+    int32_t d;      // row stride of src / dst in floats
+    int32_t width;  // columns in this tile (<= 4*G*NV)
+    int32_t accumulate;
+};
+
+// G lanes per edge, NV float4 per lane, U edges' gathers in flight per group.
+// CACHE_DST: edge list is row-sorted, keep the row-side slice in registers.
+// MASKED: the tile is narrower than 4*G*NV floats (ragged last tile).
+template <int G, int NV, int U, bool CACHE_DST, bool MASKED>
+__global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs a) {
     static_assert(G % U == 0, "U must divide G");
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
     const int gbase = lane & ~(G - 1);  // first lane of this lane's group
+    const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << gbase);
     const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
 
     int colv[NV];
@@ -45,69 +68,94 @@ sddmm_vec4_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ c
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         colv[i] = (lig + i * G) * 4;
-        ok[i] = colv[i] < d;
+        ok[i] = !MASKED || colv[i] < a.width;
+        if (!ok[i]) colv[i] = 0;
     }
-
-    int cur_row = -1;
-    float4 dcache[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) dcache[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
     for (int b = 0; b < kBatchesPerWarp; ++b) {
         const int64_t e0 = (warp * kBatchesPerWarp + b) * 32;
-        if (e0 >= nnz) break;  // warp-uniform
+        if (e0 >= a.nnz) break;  // warp-uniform
         const int64_t e = e0 + lane;
-        int r_l = -1, c_l = -1;
-        if (e < nnz) {
-            r_l = row[e];
-            c_l = col[e];
+        const bool valid = e < a.nnz;
+        int r_l = 0, c_l = 0;  // padding edges read row 0 / column 0 and are never stored
+        if (valid) {
+            r_l = a.row[e];
+            c_l = a.col[e];
         }
-        float res = 0.f;
-#pragma unroll 1
+        // bit l set: edge l starts a new row relative to edge l-1 (always set at a group's
+        // first edge so that each group loads its first row)
+        unsigned change = 0;
+        if (CACHE_DST) {
+            const int r_prev = __shfl_up_sync(0xffffffffu, r_l, 1);
+            change = __ballot_sync(0xffffffffu, lig == 0 || r_prev != r_l);
+        }
+
+        float p[G];
+        float4 dcache[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) dcache[i] = zero4;
+
+#pragma unroll
         for (int s = 0; s < G; s += U) {
-            int r[U], c[U];
+            int c[U], r[U];
             float4 xs[U][NV];
             float4 xd[U][NV];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                r[u] = __shfl_sync(0xffffffffu, r_l, gbase + s + u);
                 c[u] = __shfl_sync(0xffffffffu, c_l, gbase + s + u);
+                if (!CACHE_DST) r[u] = __shfl_sync(0xffffffffu, r_l, gbase + s + u);
             }
-#pragma unroll
-            for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    xs[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (c[u] >= 0 && ok[i]) xs[u][i] = fg::ldg4(src + (int64_t)c[u] * d + colv[i]);
-                    if (!CACHE_DST) {
-                        xd[u][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (r[u] >= 0 && ok[i])
-                            xd[u][i] = fg::ldg4(dst + (int64_t)r[u] * d + colv[i]);
-                    }
-                }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                float p = 0.f;
-                if (CACHE_DST) {
-                    if (r[u] >= 0 && r[u] != cur_row) {
-                        cur_row = r[u];
+                const float* ps = a.src + (int64_t)c[u] * a.d;
 #pragma unroll
-                        for (int i = 0; i < NV; ++i)
-                            if (ok[i]) dcache[i] = fg::ldg4(dst + (int64_t)cur_row * d + colv[i]);
+                for (int i = 0; i < NV; ++i) {
+                    xs[u][i] = fg::ldg4(ps + colv[i]);
+                    if (MASKED && !ok[i]) xs[u][i] = zero4;
+                }
+                if (!CACHE_DST) {
+                    const float* pd = a.dst + (int64_t)r[u] * a.d;
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) xd[u][i] = fg::ldg4(pd + colv[i]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                float acc = 0.f;
+                if (CACHE_DST) {
+                    if ((change >> (gbase + s + u)) & 1u) {  // uniform within the group
+                        const int rr = __shfl_sync(gmask, r_l, gbase + s + u);
+                        const float* pd = a.dst + (int64_t)rr * a.d;
+#pragma unroll
+                        for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
                     }
 #pragma unroll
-                    for (int i = 0; i < NV; ++i) p = dot4(p, xs[u][i], dcache[i]);
+                    for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], dcache[i]);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < NV; ++i) p = dot4(p, xs[u][i], xd[u][i]);
+                    for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], xd[u][i]);
                 }
-#pragma unroll
-                for (int off = G / 2; off > 0; off >>= 1)
-                    p = __fadd_rn(p, __shfl_xor_sync(0xffffffffu, p, off));
-                if (lig == s + u) res = p;
+                p[s + u] = acc;
             }
         }
-        if (e < nnz) out[e] = res;
+
+        // transposed butterfly: afterwards p[0] on lane i of the group is edge i's total
+#pragma unroll
+        for (int off = G / 2; off >= 1; off >>= 1) {
+            const bool upper = (lig & off) != 0;
+#pragma unroll
+            for (int i = 0; i < off; ++i) {
+                const float send = upper ? p[i] : p[i + off];
+                const float keep = upper ? p[i + off] : p[i];
+                p[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+        }
+        if (valid) {
+            float res = p[0];
+            if (a.accumulate) res = a.out[e] + res;
+            a.out[e] = res;
+        }
     }
 }
 
@@ -135,10 +183,9 @@ sddmm_generic_kernel(const int32_t* __restrict__ row, const int32_t* __restrict_
             const float* ps = src + (int64_t)c * d;
             const float* pd = dst + (int64_t)r * d;
             float p = 0.f;
-            for (int k = lane; k < d; k += 32) p = fg::mul_then_add(p, __ldg(ps + k), __ldg(pd + k));
+            for (int k = lane; k < d; k += 32) p = fmaf(__ldg(ps + k), __ldg(pd + k), p);
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1)
-                p = __fadd_rn(p, __shfl_xor_sync(0xffffffffu, p, off));
+            for (int off = 16; off > 0; off >>= 1) p += __shfl_xor_sync(0xffffffffu, p, off);
             if (lane == s) res = p;
         }
         if (e < nnz) out[e] = res;
@@ -146,47 +193,29 @@ sddmm_generic_kernel(const int32_t* __restrict__ row, const int32_t* __restrict_
 }
 
 template <int G, int NV, int U>
-int launch_vec4(const int32_t* row, const int32_t* col, const float* src, const float* dst,
-                float* out, int64_t nnz, int32_t d, bool cache_dst, unsigned blocks,
-                cudaStream_t s) {
-    if (cache_dst)
-        sddmm_vec4_kernel<G, NV, U, true><<<blocks, kThreads, 0, s>>>(row, col, src, dst, out, nnz, d);
-    else
-        sddmm_vec4_kernel<G, NV, U, false><<<blocks, kThreads, 0, s>>>(row, col, src, dst, out, nnz, d);
+int launch_tile(const SddmmArgs& a, bool cache_dst, bool masked, unsigned blocks, cudaStream_t s) {
+    // Variants that hold more live registers (both rows gathered per edge; masked loads) keep
+    // half as many edges in flight so that they stay within the register budget.
+    constexpr int UH = U > 1 ? U / 2 : 1;
+    if (cache_dst) {
+        if (masked)
+            sddmm_tile_kernel<G, NV, UH, true, true><<<blocks, kThreads, 0, s>>>(a);
+        else
+            sddmm_tile_kernel<G, NV, U, true, false><<<blocks, kThreads, 0, s>>>(a);
+    } else {
+        if (masked)
+            sddmm_tile_kernel<G, NV, UH, false, true><<<blocks, kThreads, 0, s>>>(a);
+        else
+            sddmm_tile_kernel<G, NV, UH, false, false><<<blocks, kThreads, 0, s>>>(a);
+    }
     FG_CUDA_TRY(cudaGetLastError());
     return FG_OK;
 }
 
-}  // namespace
-
-extern "C" {
-
-int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src,
-                     const float* d_dst, float* d_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
-                     int32_t d, int32_t rows_sorted, void* stream) {
-    if (n_rows < 0 || n_cols < 0 || nnz < 0 || d < 1)
-        return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d",
-                        (long long)n_rows, (long long)n_cols, (long long)nnz, d);
-    if (n_rows > INT32_MAX || n_cols > INT32_MAX)
-        return fg::fail(FG_ERR_INVALID_ARGUMENT, "sizes beyond int32 indexing are not supported");
-    if (nnz == 0) return FG_OK;
-    if (!d_row || !d_col || !d_src || !d_dst || !d_out)
-        return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL array argument");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int64_t edges_per_block = (int64_t)(kThreads / 32) * kBatchesPerWarp * 32;
-    const int64_t nblocks = (nnz + edges_per_block - 1) / edges_per_block;
-    if (nblocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
-    const unsigned blocks = (unsigned)nblocks;
-    const bool cache = rows_sorted != 0;
-    const bool vec = (d % 4 == 0) && d <= 512 && fg::aligned16(d_src) && fg::aligned16(d_dst);
-    if (!vec) {
-        sddmm_generic_kernel<<<blocks, kThreads, 0, s>>>(d_row, d_col, d_src, d_dst, d_out, nnz, d);
-        FG_CUDA_TRY(cudaGetLastError());
-        return FG_OK;
-    }
-#define FG_SDDMM(G, NV, U) \
-    return launch_vec4<G, NV, U>(d_row, d_col, d_src, d_dst, d_out, nnz, d, cache, blocks, s)
-    const int q = d / 4;  // float4 per feature row
+// One tile of `width` floats (a multiple of 4, at most 512).
+int launch_width(const SddmmArgs& a, bool cache, unsigned blocks, cudaStream_t s) {
+    const int q = (a.width + 3) / 4;  // float4 per edge in this tile
+#define FG_SDDMM(G, NV, U) return launch_tile<G, NV, U>(a, cache, q != (G) * (NV), blocks, s)
     if (q <= 1) FG_SDDMM(1, 1, 1);
     if (q <= 2) FG_SDDMM(2, 1, 2);
     if (q <= 4) FG_SDDMM(4, 1, 4);
@@ -197,6 +226,79 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
     if (q <= 96) FG_SDDMM(32, 3, 2);
     FG_SDDMM(32, 4, 2);
 #undef FG_SDDMM
+}
+
+int64_t l2_size_bytes() {
+    static thread_local int64_t l2 = -1;
+    if (l2 < 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) == cudaSuccess)
+            l2 = v;
+        else
+            l2 = 64ll << 20;
+    }
+    return l2;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src,
+                     const float* d_dst, float* d_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                     int32_t d, int32_t rows_sorted, int32_t feat_tile, void* stream) {
+    if (n_rows < 0 || n_cols < 0 || nnz < 0 || d < 1)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d",
+                        (long long)n_rows, (long long)n_cols, (long long)nnz, d);
+    if (n_rows > INT32_MAX || n_cols > INT32_MAX)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "sizes beyond int32 indexing are not supported");
+    if (feat_tile != 0 && (feat_tile < 4 || feat_tile > 512 || (feat_tile & (feat_tile - 1))))
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "feat_tile=%d: want 0 or a power of two in 4..512",
+                        feat_tile);
+    if (nnz == 0) return FG_OK;
+    if (!d_row || !d_col || !d_src || !d_dst || !d_out)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL array argument");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t edges_per_block = (int64_t)(kThreads / 32) * kBatchesPerWarp * 32;
+    const int64_t nblocks = (nnz + edges_per_block - 1) / edges_per_block;
+    if (nblocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
+    const unsigned blocks = (unsigned)nblocks;
+    const bool cache = rows_sorted != 0;
+    const bool vec = (d % 4 == 0) && fg::aligned16(d_src) && fg::aligned16(d_dst);
+    if (!vec) {
+        sddmm_generic_kernel<<<blocks, kThreads, 0, s>>>(d_row, d_col, d_src, d_dst, d_out, nnz, d);
+        FG_CUDA_TRY(cudaGetLastError());
+        return FG_OK;
+    }
+    // Tile width: the whole row if the column-side matrix fits the resident share of L2 (or if
+    // not even a 32-float slice does); otherwise the widest power of two whose slice fits.
+    int tile = feat_tile;
+    if (tile == 0) {
+        const int64_t budget = l2_size_bytes() / 2;
+        if (n_cols * (int64_t)d * 4 <= budget || n_cols * 32 * 4 > budget) {
+            tile = d <= 512 ? d : 512;
+        } else {
+            tile = 32;
+            while (tile * 2 <= 512 && n_cols * (int64_t)(tile * 2) * 4 <= budget) tile *= 2;
+        }
+    }
+    if (tile > d) tile = d;
+    SddmmArgs a;
+    a.row = d_row;
+    a.col = d_col;
+    a.out = d_out;
+    a.nnz = nnz;
+    a.d = d;
+    for (int f0 = 0; f0 < d; f0 += tile) {
+        a.src = d_src + f0;
+        a.dst = d_dst + f0;
+        a.width = (d - f0 < tile) ? d - f0 : tile;
+        a.accumulate = f0 > 0;
+        const int rc = launch_width(a, cache, blocks, s);
+        if (rc != FG_OK) return rc;
+    }
+    return FG_OK;
 }
 
 }  // extern "C"

@@ -19,7 +19,15 @@
 // Balance.  Rows are visited in the order of an fg_row_schedule (heaviest first), blocks
 // are launched in that order, and the groups sharing a warp hold neighbouring (hence
 // similar-length) rows, so the warp-uniform loop below wastes few iterations.
+//
+// Long rows.  A row cannot be split between workers (its sum is sequential), so the time of
+// the longest row is a floor under the whole launch: with 8 gathers in flight a 20,000-nonzero
+// row costs 2,500 dependent round trips to L2.  Rows the schedule marks as long therefore go
+// to spmm_long_rows_kernel, which keeps a ring of kDeep x 8 gathers in flight per lane (the
+// same sums, a deeper pipeline), and is launched first; the remaining rows follow in
+// spmm_rows_kernel.
 #include "common.cuh"
+#include "schedule.cuh"
 
 namespace {
 
@@ -32,6 +40,8 @@ struct SpmmArgs {
     const float* x;
     float* out;
     const int32_t* order;  // row visiting order or nullptr
+    int32_t order_begin;   // this launch covers order[order_begin, order_begin + n_sched)
+    int32_t n_sched;
     int32_t n_rows;
     int32_t d;
     int32_t n_tiles;
@@ -84,13 +94,13 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
     const int64_t unit = (int64_t)blockIdx.x * (kThreads / G) + (threadIdx.x / G);
-    const int64_t n_units = (int64_t)a.n_rows * a.n_tiles;
+    const int64_t n_units = (int64_t)a.n_sched * a.n_tiles;
     const bool live = unit < n_units;
 
     int row = 0, tile = 0;
     if (live) {
-        tile = (int)(unit / a.n_rows);
-        const int p = (int)(unit - (int64_t)tile * a.n_rows);
+        tile = (int)(unit / a.n_sched);
+        const int p = a.order_begin + (int)(unit - (int64_t)tile * a.n_sched);
         row = a.order ? a.order[p] : p;
     }
     const int col = tile * (G * VEC) + lig * VEC;
@@ -163,9 +173,114 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
     if (col_ok) total.store(a.out + (int64_t)row * a.d + col);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Long rows: 8 lanes per (row, 32-float tile) unit, 128-bit gathers, and a register ring of
+// kDeep chunks of 8 gathers per lane.  Slot s of the ring holds chunk q (q % kDeep == s); when
+// chunk q has been added, the gathers of chunk q + kDeep are issued into the same slot, using
+// column ids that were fetched one ring revolution earlier, and the ids / values of chunk
+// q + 2*kDeep are requested.  The adds themselves run in storage order exactly as in
+// spmm_rows_kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int kDeep = 4;
+constexpr int kLongThreads = 64;
+
+__global__ void __launch_bounds__(kLongThreads, 6) spmm_long_rows_kernel(const SpmmArgs a) {
+    constexpr int G = 8, CH = 8;
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (G - 1);
+    const int64_t unit = (int64_t)blockIdx.x * (kLongThreads / G) + (threadIdx.x / G);
+    const int64_t n_units = (int64_t)a.n_sched * a.n_tiles;
+    const bool live = unit < n_units;
+    int row = 0, tile = 0;
+    if (live) {
+        tile = (int)(unit / a.n_sched);
+        row = a.order[a.order_begin + (int)(unit - (int64_t)tile * a.n_sched)];
+    }
+    const int col = tile * 32 + lig * 4;
+    const bool col_ok = live && col < a.d;
+    const float* xcol = a.x + (col_ok ? col : 0);
+    int start = 0, len = 0;
+    if (live) {
+        start = a.pos[row];
+        len = a.pos[row + 1] - start;
+    }
+    const int n_chunks = __reduce_max_sync(0xffffffffu, (len + CH - 1) / CH);
+    const int full_chunks = __reduce_min_sync(0xffffffffu, len / CH);  // chunks with no padding
+
+    Slice<4> acc;
+    acc.zero();
+    Slice<4> ring[kDeep][CH];
+    float v_now[kDeep];   // this lane's value of the chunk sitting in the slot
+    int c_next[kDeep];    // this lane's column id / value of the chunk that enters the slot next
+    float v_next[kDeep];
+
+    auto fetch_ids = [&](int q, int& c, float& v) {
+        const int k = q * CH + lig;
+        c = -1;
+        v = 0.f;
+        if (k < len) {
+            c = a.idx[start + k];
+            v = a.vals[start + k];
+        }
+    };
+    auto issue = [&](int slot, int c_mine) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            const int c = __shfl_sync(0xffffffffu, c_mine, j, G);
+            ring[slot][j].load(xcol + (int64_t)(c < 0 ? 0 : c) * a.d);
+        }
+    };
+
+    // prologue: fill the ring, then request the ids of the next revolution
+#pragma unroll
+    for (int s = 0; s < kDeep; ++s) {
+        int c;
+        fetch_ids(s, c, v_now[s]);
+        if (s < n_chunks) issue(s, c);
+    }
+#pragma unroll
+    for (int s = 0; s < kDeep; ++s) fetch_ids(kDeep + s, c_next[s], v_next[s]);
+
+    for (int q0 = 0; q0 < n_chunks; q0 += kDeep) {
+#pragma unroll
+        for (int s = 0; s < kDeep; ++s) {
+            const int q = q0 + s;
+            if (q >= n_chunks) break;  // warp-uniform
+            if (q < full_chunks) {
+#pragma unroll
+                for (int j = 0; j < CH; ++j)
+                    acc.axpy(__shfl_sync(0xffffffffu, v_now[s], j, G), ring[s][j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    Slice<4> next = acc;
+                    next.axpy(__shfl_sync(0xffffffffu, v_now[s], j, G), ring[s][j]);
+                    acc.select(q * CH + j < len, next);
+                }
+            }
+            if (q + kDeep < n_chunks) issue(s, c_next[s]);
+            v_now[s] = v_next[s];
+            fetch_ids(q + 2 * kDeep, c_next[s], v_next[s]);
+        }
+    }
+    if (col_ok) acc.store(a.out + (int64_t)row * a.d + col);
+}
+
+int launch_long(const SpmmArgs& a, cudaStream_t s) {
+    const int64_t n_units = (int64_t)a.n_sched * a.n_tiles;
+    const int64_t units_per_block = kLongThreads / 8;
+    const int64_t blocks = (n_units + units_per_block - 1) / units_per_block;
+    if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
+    if (blocks == 0) return FG_OK;
+    spmm_long_rows_kernel<<<(unsigned)blocks, kLongThreads, 0, s>>>(a);
+    FG_CUDA_TRY(cudaGetLastError());
+    return FG_OK;
+}
+
 template <int G, int VEC>
 int launch(const SpmmArgs& a, bool dds, cudaStream_t s) {
-    const int64_t n_units = (int64_t)a.n_rows * a.n_tiles;
+    const int64_t n_units = (int64_t)a.n_sched * a.n_tiles;
     const int64_t units_per_block = kThreads / G;
     const int64_t blocks = (n_units + units_per_block - 1) / units_per_block;
     if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
@@ -229,6 +344,8 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     a.x = x;
     a.out = out;
     a.order = schedule ? fg_row_schedule_order(schedule) : nullptr;
+    a.order_begin = 0;
+    a.n_sched = (int32_t)n_rows;
     a.n_rows = (int32_t)n_rows;
     a.d = d;
     a.parts = parts;
@@ -240,6 +357,18 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
         // scalar path: 32 lanes x 1 float per unit
         a.n_tiles = (d + 31) / 32;
         return launch<32, 1>(a, dds, s);
+    }
+    // long rows first, through the deep pipeline (CSR with a schedule only)
+    const int64_t n_long = (schedule && !dds) ? schedule->n_long : 0;
+    if (n_long > 0) {
+        SpmmArgs h = a;
+        h.n_sched = (int32_t)n_long;
+        h.n_tiles = (d + 31) / 32;
+        const int rc = launch_long(h, s);
+        if (rc != FG_OK) return rc;
+        a.order_begin = (int32_t)n_long;
+        a.n_sched = (int32_t)(n_rows - n_long);
+        if (a.n_sched == 0) return FG_OK;
     }
     int tile = feat_tile ? feat_tile : auto_tile(n_cols, d);
     const int cap = fg::pow2_ceil(d);

@@ -52,6 +52,7 @@ class SDDMMbase:
                                                 dev.stream_ptr(self._device)))
         self._rows_sorted = int(sorted_flag.value)
         self._shapes = None
+        self._feat_tile = 0
         self.out = None
 
     def _register(self):
@@ -85,6 +86,13 @@ class SDDMMbase:
         if nfp < 1 or d % nfp != 0:
             raise ValueError("feat_len %d is not divisible by num_feat_partitions %d" % (d, nfp))
         self._check_schedule(schedule_args, nfp)
+        tile = int(schedule_args.get("feat_tile", 0))
+        if tile == 0 and nfp > 1:
+            # the reference's feature tiling knob doubles as the L2 tile width when it is usable
+            f = d // nfp
+            if 4 <= f <= 512 and (f & (f - 1)) == 0:
+                tile = f
+        self._planned_tile = tile
         return src_shape, dst_shape, d, nfp
 
     def _check_schedule(self, schedule_args, nfp):
@@ -94,6 +102,7 @@ class SDDMMbase:
         """Fix the feature shapes and allocate the (reused) per-edge output (reference :72-92)."""
         src_shape, dst_shape, _, _ = self._plan(input_placeholders, compute_args, schedule_args)
         self._shapes = (src_shape, dst_shape)
+        self._feat_tile = self._planned_tile
         self.out = torch.zeros((self._nnz,), dtype=torch.float32, device=self._device)
 
     def lower_to_ir(self, input_placeholders, compute_args, schedule_args):
@@ -110,7 +119,8 @@ class SDDMMbase:
         dev.check(dev.lib().fg_sddmm_coo_f32(dev.ptr(self._adj_row), dev.ptr(self._adj_col),
                                              dev.ptr(src), dev.ptr(dst), dev.ptr(out),
                                              self._num_rows, self._num_cols, self._nnz, d,
-                                             self._rows_sorted, dev.stream_ptr(self._device)))
+                                             self._rows_sorted, self._feat_tile,
+                                             dev.stream_ptr(self._device)))
 
     def run(self, inputs):
         """Enqueue the kernel on the current stream; returns the module's output tensor (the
@@ -164,7 +174,7 @@ class VanillaSDDMMx86(SDDMMbase):
     """The x86 class of the reference (python/featgraph/module/sddmm.py:168-176)."""
 
     _compute_keys = ("num_feat_partitions",)
-    _schedule_keys = ("num_feat_partitions",)
+    _schedule_keys = ("num_feat_partitions", "feat_tile")
 
     def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device=None):
         super().__init__(adj_scipy, num_row_partitions, num_col_partitions, device)
@@ -179,7 +189,7 @@ class VanillaSDDMMcuda(SDDMMbase):
     (python/featgraph/op/vanilla_sddmm.py:79-82) and otherwise has no effect."""
 
     _compute_keys = ()
-    _schedule_keys = ("num_feat_partitions", "num_cuda_blocks")
+    _schedule_keys = ("num_feat_partitions", "num_cuda_blocks", "feat_tile")
 
     def __init__(self, adj_scipy, device=None):
         super().__init__(adj_scipy, 1, 1, device)

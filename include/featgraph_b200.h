@@ -65,6 +65,9 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream
 /* Device pointer to the n_rows row ids in visiting order (valid until destroy). */
 const int32_t* fg_row_schedule_order(const fg_row_schedule* schedule);
 int64_t fg_row_schedule_num_rows(const fg_row_schedule* schedule);
+/* How many rows at the front of the order are "long" (>= 1024 nonzeros): SpMM runs those
+ * with a deeper gather pipeline so that one long sequential row does not set the run time. */
+int64_t fg_row_schedule_num_long_rows(const fg_row_schedule* schedule);
 void fg_row_schedule_destroy(fg_row_schedule* schedule);
 
 /* --------------------------------------------------------------------------------------
@@ -105,13 +108,18 @@ int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
  *   rows_sorted  non-zero promises that d_row is non-decreasing (a CSR-ordered edge list):
  *                the row-side feature row is then kept in registers across a row's edges.
  *                Zero is always safe.
- * src: [n_cols, d], dst: [n_rows, d], out: [nnz].  The dot product is summed as a fixed
- * tree (per-lane partial sums, then a butterfly), not in ascending k; the difference from
- * the sequential sum is bounded by fp32 rounding of d terms.
+ *   feat_tile    width in floats of the feature slice handled per pass over the edges (power
+ *                of two, 4..512), 0 = the whole row if the column-side matrix fits in L2, else
+ *                the widest slice that does.  With more than one pass, pass t > 0 adds its
+ *                partial dot product to out[e]: the reference's num_feat_partitions loop
+ *                order (op/vanilla_sddmm.py:70-72).
+ * src: [n_cols, d], dst: [n_rows, d], out: [nnz].  The dot product is summed with FMAs as a
+ * fixed tree (per-lane partial sums, then a butterfly; tiles in ascending order), not in
+ * ascending k; the difference from the sequential sum is bounded by fp32 rounding of d terms.
  * -------------------------------------------------------------------------------------- */
 int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src,
                      const float* d_dst, float* d_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
-                     int32_t d, int32_t rows_sorted, void* stream);
+                     int32_t d, int32_t rows_sorted, int32_t feat_tile, void* stream);
 
 /* --------------------------------------------------------------------------------------
  * Index checks (the code generator of the reference emits shape asserts only; these add

@@ -79,14 +79,14 @@ def spmm_dds(s1_pos, s1_idx, vals, x, n_rows, parts, indptr_for_schedule=None, f
     return out.cpu().numpy().reshape(n_rows, d)
 
 
-def sddmm(row, col, src, dst, rows_sorted=0):
+def sddmm(row, col, src, dst, rows_sorted=0, feat_tile=0):
     L = _native.lib()
     n_cols, d = src.shape
     n_rows = dst.shape[0]
     rr, cc, ss, dd = dev(row, np.int32), dev(col, np.int32), dev(src, np.float32), dev(dst, np.float32)
     buf, out = guarded(len(row))
     _native.check(L.fg_sddmm_coo_f32(p(rr), p(cc), p(ss), p(dd), p(out), n_rows, n_cols, len(row), d,
-                                     int(rows_sorted), stream()))
+                                     int(rows_sorted), int(feat_tile), stream()))
     torch.cuda.synchronize()
     assert guards_intact(buf), "kernel wrote outside its output"
     return out.cpu().numpy()

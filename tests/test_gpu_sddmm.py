@@ -37,6 +37,18 @@ def test_feature_lengths_and_edge_orders(oracle, d, order):
         np.testing.assert_allclose(G.sddmm(row, col, src, dst, rows_sorted=1), want, rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("d,tile", [(128, 32), (128, 64), (100, 32), (256, 64), (512, 128), (96, 64), (640, 0)])
+def test_feature_tiles_accumulate_to_the_same_dot_product(oracle, d, tile):
+    import gpu_util as G
+    coo = sp.random(200, 150, density=0.1, format="csr", random_state=d + tile).tocoo()
+    row, col = coo.row.astype(np.int32), coo.col.astype(np.int32)
+    src, dst = _feat(150, d, 3), _feat(200, d, 4)
+    want = oracle.sddmm(row, col, src, dst)
+    for s in (0, 1):
+        np.testing.assert_allclose(G.sddmm(row, col, src, dst, rows_sorted=s, feat_tile=tile), want,
+                                   rtol=RTOL, atol=ATOL)
+
+
 def test_exact_on_small_integers():
     """Integer-valued features make every fp32 operation exact, whatever the summation tree."""
     import gpu_util as G

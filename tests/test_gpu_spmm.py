@@ -85,6 +85,31 @@ def test_one_very_long_row_among_short_ones(oracle):
         np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x), want)
 
 
+@pytest.mark.parametrize("d", [4, 32, 36, 100, 128, 33])
+def test_long_rows_take_the_deep_pipeline_and_stay_exact(oracle, d):
+    """Rows of 1024+ nonzeros run in the long-row kernel: lengths around the chunk (8) and ring
+    (32) sizes, a mix with short rows, and random (non-unit) values."""
+    import gpu_util as G
+    from featgraph_b200 import graphgen
+    deg = np.array([1024, 1025, 1031, 1032, 1056, 2048, 5000, 1023, 0, 7, 1055, 3001, 1, 1040], dtype=np.int64)
+    a = graphgen._csr_from_degrees(deg, 6000, seed=77)
+    a.data = (np.random.default_rng(78).random(a.nnz, dtype=np.float32) * 2 - 1).astype(np.float32)
+    x = graphgen.uniform_features((6000, d), seed=79 + d)
+    want = oracle.spmm_csr(a.indptr, a.indices, a.data, x)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x), want)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x, feat_tile=32), want)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x, use_schedule=False), want)
+
+
+def test_every_row_long(oracle):
+    import gpu_util as G
+    from featgraph_b200 import graphgen
+    a = graphgen._csr_from_degrees(np.full(37, 1500, dtype=np.int64), 4000, seed=5)
+    x = graphgen.uniform_features((4000, 64), seed=6)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x),
+                                  oracle.spmm_csr(a.indptr, a.indices, a.data, x))
+
+
 def test_unsorted_and_duplicate_columns_keep_storage_order(oracle):
     import gpu_util as G
     rng = np.random.default_rng(5)
@@ -135,6 +160,13 @@ def test_row_schedule_is_degree_descending_and_stable():
     order = _device.view_device_int32(addr, 5000, torch.device("cuda", torch.cuda.current_device())).cpu().numpy()
     want = np.argsort(-deg, kind="stable")
     np.testing.assert_array_equal(order, want)
+    assert _native.lib().fg_row_schedule_num_long_rows(sch.h) == 0
+    sch.close()
+    deg[[5, 4000, 77]] = [1024, 3000, 1023]
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+    sch = G.Schedule(G.dev(indptr), 5000)
+    assert _native.lib().fg_row_schedule_num_long_rows(sch.h) == 2
+    assert _native.lib().fg_row_schedule_num_rows(sch.h) == 5000
     sch.close()
 
 
