@@ -18,7 +18,7 @@ SIGNATURES = {
     "fg_version": (ctypes.c_int, []),
     "fg_last_error": (ctypes.c_char_p, []),
     "fg_device_info": (ctypes.c_int, [_vp, _vp, _vp, _vp]),
-    "fg_row_schedule_create": (ctypes.c_int, [_vp, _i64, _vp, _vp]),
+    "fg_row_schedule_create": (ctypes.c_int, [_vp, _i64, _i32, _vp, _vp]),
     "fg_row_schedule_order": (_vp, [_vp]),
     "fg_row_schedule_num_rows": (_i64, [_vp]),
     "fg_row_schedule_num_long_rows": (_i64, [_vp]),

@@ -35,13 +35,17 @@ __global__ void count_long_rows_kernel(const uint32_t* __restrict__ sorted_keys,
 
 extern "C" {
 
-int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream,
-                           fg_row_schedule** out_schedule) {
+int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long_row_threshold,
+                           void* stream, fg_row_schedule** out_schedule) {
     if (!out_schedule) return fg::fail(FG_ERR_INVALID_ARGUMENT, "out_schedule is NULL");
     *out_schedule = nullptr;
     if (n_rows < 0 || n_rows > INT32_MAX)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "n_rows=%lld out of range", (long long)n_rows);
     if (n_rows > 0 && !d_indptr) return fg::fail(FG_ERR_INVALID_ARGUMENT, "d_indptr is NULL");
+    if (long_row_threshold < 0)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "long_row_threshold must be >= 0 (0 = default)");
+    const uint32_t threshold =
+        long_row_threshold > 0 ? (uint32_t)long_row_threshold : fg::kLongRowThreshold;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     fg_row_schedule* sch = new fg_row_schedule();
     sch->n_rows = n_rows;
@@ -53,6 +57,7 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream
     int32_t* rows_in = nullptr;
     int32_t* d_n_long = nullptr;
     int32_t h_n_long = 0;
+    uint32_t h_max_key = 0;
     void* temp = nullptr;
     size_t temp_bytes = 0;
     int rc = FG_OK;
@@ -92,11 +97,13 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, void* stream
         temp, temp_bytes, keys_in, keys_out, rows_in, sch->d_order, (int)n_rows, 0, 32, s));
     FG_TRY_OR_CLEAN(cudaMalloc(&d_n_long, sizeof(int32_t)));
     FG_TRY_OR_CLEAN(cudaMemsetAsync(d_n_long, 0, sizeof(int32_t), s));
-    count_long_rows_kernel<<<blocks, threads, 0, s>>>(keys_out, n_rows, fg::kLongRowThreshold, d_n_long);
+    count_long_rows_kernel<<<blocks, threads, 0, s>>>(keys_out, n_rows, threshold, d_n_long);
     FG_TRY_OR_CLEAN(cudaGetLastError());
     FG_TRY_OR_CLEAN(cudaMemcpyAsync(&h_n_long, d_n_long, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    FG_TRY_OR_CLEAN(cudaMemcpyAsync(&h_max_key, keys_out, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
     FG_TRY_OR_CLEAN(cudaStreamSynchronize(s));
     sch->n_long = h_n_long;
+    sch->max_row_nnz = h_max_key;
 #undef FG_TRY_OR_CLEAN
     cleanup();
     *out_schedule = sch;

@@ -12,4 +12,5 @@ struct fg_row_schedule {
     int32_t* d_order = nullptr;  // row ids, nonzero count descending, ties in row order
     int64_t n_rows = 0;
     int64_t n_long = 0;  // the first n_long entries of d_order are long rows
+    int64_t max_row_nnz = 0;
 };

@@ -184,6 +184,10 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
 // ---------------------------------------------------------------------------------------------
 constexpr int kDeep = 4;
 constexpr int kLongThreads = 64;
+// Measured on B200: a dependent batch of 8 gathers in spmm_rows_kernel costs about 0.6 us under
+// load (a 20,000-nonzero row alone takes 1.5 ms), and gathers stream from L2 at about 17 TB/s.
+constexpr double kRoundTripSeconds = 0.6e-6;
+constexpr double kGatherBytesPerSecond = 17e12;
 
 __global__ void __launch_bounds__(kLongThreads, 6) spmm_long_rows_kernel(const SpmmArgs a) {
     constexpr int G = 8, CH = 8;
@@ -358,8 +362,15 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
         a.n_tiles = (d + 31) / 32;
         return launch<32, 1>(a, dds, s);
     }
-    // long rows first, through the deep pipeline (CSR with a schedule only)
-    const int64_t n_long = (schedule && !dds) ? schedule->n_long : 0;
+    // Long rows first, through the deep pipeline (CSR with a schedule only), when the longest
+    // row would otherwise set the run time: its estimated time in spmm_rows_kernel (one round
+    // trip to L2 per 8 nonzeros) against the whole launch's time at the SM<-L2 gather rate.
+    int64_t n_long = (schedule && !dds) ? schedule->n_long : 0;
+    if (n_long > 0) {
+        const double t_longest_row = (double)schedule->max_row_nnz / 8.0 * kRoundTripSeconds;
+        const double gathered_bytes = 4.0 * (double)nnz * d + 8.0 * (double)nnz * ((d + 63) / 64);
+        if (t_longest_row < gathered_bytes / kGatherBytesPerSecond) n_long = 0;
+    }
     if (n_long > 0) {
         SpmmArgs h = a;
         h.n_sched = (int32_t)n_long;

@@ -23,7 +23,7 @@ class SpMMbase:
     _compute_keys = ()
     _schedule_keys = ()
 
-    def __init__(self, adj_scipy, num_col_partitions=1, device=None):
+    def __init__(self, adj_scipy, num_col_partitions=1, device=None, long_row_threshold=0):
         # CSR in SpMM-like kernels (reference :26-29)
         adj_csr = adj_scipy.tocsr() if adj_scipy.format != "csr" else adj_scipy
         self._num_rows, self._num_cols = adj_csr.shape
@@ -48,6 +48,7 @@ class SpMMbase:
             # heavy-rows-first visiting order, shared by the CSR and DDS kernels
             self._schedule = ctypes.c_void_p()
             dev.check(L.fg_row_schedule_create(dev.ptr(indptr), self._num_rows,
+                                               int(long_row_threshold),
                                                dev.stream_ptr(self._device),
                                                ctypes.byref(self._schedule)))
             if self._num_col_partitions > 1:
@@ -217,8 +218,8 @@ class VanillaSpMMcuda(SpMMbase):
     _compute_keys = ()
     _schedule_keys = ("num_cuda_blocks", "num_threads_per_cuda_block", "feat_tile")
 
-    def __init__(self, adj_scipy, device=None):
-        super().__init__(adj_scipy, 1, device)
+    def __init__(self, adj_scipy, device=None, long_row_threshold=0):
+        super().__init__(adj_scipy, 1, device, long_row_threshold)
 
     def _register(self):
         self._target = "cuda"

@@ -20,9 +20,10 @@ def stream():
 
 
 class Schedule:
-    def __init__(self, indptr_dev, n_rows):
+    def __init__(self, indptr_dev, n_rows, long_row_threshold=0):
         self.h = ctypes.c_void_p()
-        _native.check(_native.lib().fg_row_schedule_create(p(indptr_dev), n_rows, stream(), ctypes.byref(self.h)))
+        _native.check(_native.lib().fg_row_schedule_create(p(indptr_dev), n_rows, long_row_threshold, stream(),
+                                                           ctypes.byref(self.h)))
 
     def close(self):
         if self.h.value:

@@ -1,0 +1,85 @@
+"""Host-side logic of the multi-GPU layer on CPU ranks (gloo, world size 2 and 3): row ranges,
+local CSR slices and the uneven all-gather of feature rows.  The per-rank compute is done by
+the CPU oracle here (the GPU kernels are exercised by the -m gpu tests); what is checked is that
+sharding plus gathering reproduces the single-process result bit for bit."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, tmpdir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from featgraph_b200 import graphgen
+        from featgraph_b200.sharded import all_gather_rows, shard_csr_rows
+        from featgraph_b200.util import nnz_balanced_row_ranges
+
+        n, d = 600, 24
+        adj = graphgen.power_law_graph(n, 30_000, seed=11, kmax=500)
+        x = graphgen.uniform_features((n, d), seed=12)
+        y = graphgen.uniform_features((n, d), seed=13)
+        bounds = nnz_balanced_row_ranges(adj.indptr, world)
+        lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+
+        local = shard_csr_rows(adj, bounds, rank)
+        assert local.shape == (hi - lo, n) and local.indptr[0] == 0
+        assert local.indptr.dtype == np.int32 and local.indices.dtype == np.int32
+        np.testing.assert_array_equal(local.indices, adj.indices[adj.indptr[lo]:adj.indptr[hi]])
+        # a rank can also generate its rows alone and get the same slice
+        alone = graphgen.power_law_graph(n, 30_000, seed=11, kmax=500, rows=(lo, hi))
+        np.testing.assert_array_equal(alone.indices, local.indices)
+        np.testing.assert_array_equal(alone.indptr, local.indptr)
+
+        # uneven all-gather of the feature rows
+        full = torch.full((n, d), float("nan"))
+        all_gather_rows(full, torch.from_numpy(x[lo:hi].copy()), bounds)
+        np.testing.assert_array_equal(full.numpy(), x)
+
+        # per-rank SpMM on the gathered features == rows [lo, hi) of the whole product
+        whole = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)
+        mine = oracle.spmm_csr(local.indptr, local.indices, local.data, full.numpy())
+        np.testing.assert_array_equal(mine, whole[lo:hi])
+
+        # per-rank SDDMM: edges of the local rows, row-side features local, column-side gathered
+        coo = adj.tocoo()
+        whole_e = oracle.sddmm(coo.row, coo.col, x, y)
+        lc = local.tocoo()
+        mine_e = oracle.sddmm(lc.row, lc.col, full.numpy(), y[lo:hi])
+        np.testing.assert_array_equal(mine_e, whole_e[adj.indptr[lo]:adj.indptr[hi]])
+
+        # wrong-sized local block is refused before any communication
+        with pytest.raises(ValueError):
+            all_gather_rows(full, torch.zeros(hi - lo + 1, d), bounds)
+        open(os.path.join(tmpdir, "ok%d" % rank), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharding_and_gather_on_cpu_ranks(tmp_path, world):
+    import oracle
+    oracle.build()  # once, before the ranks race to build it
+    from featgraph_b200 import build
+    build.build_graphgen()
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok%d" % r for r in range(world)]
