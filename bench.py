@@ -34,10 +34,32 @@ def log(*a):
     print(*a, file=sys.stderr, flush=True)
 
 
+_JSON_FD = None
+
+
+def protect_stdout():
+    """Keep stdout for the one JSON line: libraries that chat on fd 1 (NCCL prints its version
+    banner there) are sent to stderr instead."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
+
+
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=5)
+    p.add_argument("--steps", type=int, default=20)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--dims", default="32,64,128,256,512")
@@ -169,6 +191,10 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torch.distributed.run pins OMP_NUM_THREADS=1 for its workers; this arm is meant to use every
+    # host thread it can, so undo that before the OpenMP runtime is loaded.
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    protect_stdout()
     from featgraph_b200 import graphgen
     n, nnz, kmax = graph_params(args.shrink)
     t0 = time.time()
@@ -197,7 +223,7 @@ def run_reference_arm(args):
         "e2e": {"value": r["step_gflops"], "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": wall,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -210,6 +236,7 @@ def run_ours(args):
     from featgraph_b200.sharded import ShardedSDDMM, ShardedSpMM
     from featgraph_b200.util import nnz_balanced_row_ranges
 
+    protect_stdout()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -400,7 +427,7 @@ def run_ours(args):
                       "first %d edges on one thread (the reference's x86 SDDMM has no parallel loop); "
                       "1 warm-up + 1 timed run each" % r["sddmm_edges"],
             "detail": r, "wall_s": time.time() - t0}
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
