@@ -29,7 +29,7 @@
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kBatchesPerWarp = 8;  // 8 x 32 consecutive edges per warp
+constexpr int kBatchesPerWarp = 16;  // 16 x 32 consecutive edges per warp
 
 __device__ __forceinline__ float dot4(float acc, const float4& a, const float4& b) {
     acc = fmaf(a.x, b.x, acc);
@@ -73,16 +73,28 @@ __global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs
     }
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 
+    // ids of the first batch; each batch then requests the next one's before it starts gathering,
+    // so the id fetch (a DRAM stream) overlaps the previous batch instead of preceding the gathers
+    const int64_t first = warp * kBatchesPerWarp * 32;
+    int r_n = 0, c_n = 0;  // padding edges read row 0 / column 0 and are never stored
+    if (first + lane < a.nnz) {
+        r_n = a.row[first + lane];
+        c_n = a.col[first + lane];
+    }
     for (int b = 0; b < kBatchesPerWarp; ++b) {
-        const int64_t e0 = (warp * kBatchesPerWarp + b) * 32;
+        const int64_t e0 = first + (int64_t)b * 32;
         if (e0 >= a.nnz) break;  // warp-uniform
         const int64_t e = e0 + lane;
         const bool valid = e < a.nnz;
-        int r_l = 0, c_l = 0;  // padding edges read row 0 / column 0 and are never stored
-        if (valid) {
-            r_l = a.row[e];
-            c_l = a.col[e];
+        const int r_l = r_n, c_l = c_n;
+        r_n = 0;
+        c_n = 0;
+        if (b + 1 < kBatchesPerWarp && e + 32 < a.nnz) {
+            r_n = a.row[e + 32];
+            c_n = a.col[e + 32];
         }
+        float prev = 0.f;  // earlier tiles' partial dot product
+        if (a.accumulate && valid) prev = a.out[e];
         // bit l set: edge l starts a new row relative to edge l-1 (always set at a group's
         // first edge so that each group loads its first row)
         unsigned change = 0;
@@ -151,11 +163,7 @@ __global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs
                 p[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
             }
         }
-        if (valid) {
-            float res = p[0];
-            if (a.accumulate) res = a.out[e] + res;
-            a.out[e] = res;
-        }
+        if (valid) a.out[e] = prev + p[0];
     }
 }
 
@@ -275,8 +283,11 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
     // not even a 32-float slice does); otherwise the widest power of two whose slice fits.
     int tile = feat_tile;
     if (tile == 0) {
-        const int64_t budget = l2_size_bytes() / 2;
-        if (n_cols * (int64_t)d * 4 <= budget || n_cols * 32 * 4 > budget) {
+        // A single pass wins whenever the whole matrix is about L2-sized (no second read of
+        // the edge list, no read-modify-write of out); a slice should fit in half of L2.
+        const int64_t l2 = l2_size_bytes();
+        const int64_t budget = l2 / 2;
+        if (n_cols * (int64_t)d * 4 <= l2 - l2 / 20 || n_cols * 32 * 4 > budget) {
             tile = d <= 512 ? d : 512;
         } else {
             tile = 32;
