@@ -291,18 +291,22 @@ def run_ours(args):
         for d in dims:
             xd, yd = dev_feats[d]
             spmm.build_cached(d, args.feat_tile)
-            if record is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e2 = torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-            spmm.run(xd)
-            if record is not None:
-                e1.record(stream)
             sddmm.build_cached(d)
-            sddmm.run(xd, yd)
-            if record is not None:
-                e2.record(stream)
-                record.append((d, e0, e1, e2))
+            if record is None:
+                spmm.run(xd)
+                sddmm.run(xd, yd)
+                continue
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+            ev[0].record(stream)
+            spmm.gather(xd)
+            ev[1].record(stream)
+            spmm.compute()
+            ev[2].record(stream)
+            sddmm.gather(xd)
+            ev[3].record(stream)
+            sddmm.compute(yd)
+            ev[4].record(stream)
+            record.append((d, ev))
 
     # build() allocates; keep one built state per feature length so that a step only launches
     _install_build_cache(spmm, sddmm)
@@ -324,9 +328,13 @@ def run_ours(args):
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_start.elapsed_time(t_stop)
-    for d, e0, e1, e2 in records:
-        per_kernel[("spmm", d)].append(e0.elapsed_time(e1))
-        per_kernel[("sddmm", d)].append(e1.elapsed_time(e2))
+    gather_ms = {("spmm", d): [] for d in dims}
+    gather_ms.update({("sddmm", d): [] for d in dims})
+    for d, ev in records:
+        gather_ms[("spmm", d)].append(ev[0].elapsed_time(ev[1]))
+        per_kernel[("spmm", d)].append(ev[1].elapsed_time(ev[2]))
+        gather_ms[("sddmm", d)].append(ev[2].elapsed_time(ev[3]))
+        per_kernel[("sddmm", d)].append(ev[3].elapsed_time(ev[4]))
     if world > 1:
         t = torch.tensor([total_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -383,8 +391,14 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         bt = bytes_touched(n, nnz, d)
+        g_ms = float(np.mean(gather_ms[(op, d)]))
+        if world > 1:
+            t = torch.tensor([g_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            g_ms = float(t.item())
         kernels.append({
-            "op": op, "d": d, "ms": ms, "gflops": 2.0 * nnz * d / (ms * 1e-3) / 1e9,
+            "op": op, "d": d, "ms": ms, "all_gather_ms": g_ms if world > 1 else 0.0,
+            "gflops": 2.0 * nnz * d / (ms * 1e-3) / 1e9,
             "touched_gbs": bt / (ms * 1e-3) / 1e9, "frac_touched": bt / (ms * 1e-3) / 1e9 / peak,
             "frac_compulsory": bytes_unique(n, n, nnz, d) / (ms * 1e-3) / 1e9 / peak,
         })
@@ -403,7 +417,7 @@ def run_ours(args):
                 "kernel time; gathers served from L2 make it exceed DRAM traffic, see traffic",
     }
     if world > 1:
-        roofline["note"] += "; per-kernel times at N>1 include the feature all-gather"
+        roofline["note"] += "; per-kernel times are the slowest rank's kernel on its shard, with whole-graph bytes"
     line = {
         "metric": "spmm_sddmm_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,

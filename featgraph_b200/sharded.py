@@ -96,10 +96,18 @@ class ShardedSpMM(_ShardedBase):
         self.module.build([placeholder((self.n, feat_len))], {}, {"feat_tile": feat_tile})
         self.x_full = torch.empty((self.n, feat_len), dtype=torch.float32, device=self.device)
 
+    def gather(self, x_local):
+        """The exchange step alone: every rank's feature rows into this rank's ``x_full``."""
+        return self._gather(self.x_full, x_local)
+
+    def compute(self):
+        """The local kernel alone, on the features gathered last."""
+        return self.module.run([self.x_full])
+
     def run(self, x_local):
         """x_local: this rank's rows of the feature matrix.  Returns this rank's rows of A.X."""
-        self._gather(self.x_full, x_local)
-        return self.module.run([self.x_full])
+        self.gather(x_local)
+        return self.compute()
 
 
 class ShardedSDDMM(_ShardedBase):
@@ -119,8 +127,14 @@ class ShardedSDDMM(_ShardedBase):
         self.module.build([placeholder((self.n, feat_len)), placeholder((self.row_hi - self.row_lo, feat_len))], {}, {})
         self.src_full = torch.empty((self.n, feat_len), dtype=torch.float32, device=self.device)
 
+    def gather(self, src_local):
+        return self._gather(self.src_full, src_local)
+
+    def compute(self, dst_local):
+        return self.module.run([self.src_full, dst_local])
+
     def run(self, src_local, dst_local):
         """src_local: this rank's rows of the column-side matrix (gathered from all ranks);
         dst_local: this rank's rows of the row-side matrix.  Returns this rank's edges' dots."""
-        self._gather(self.src_full, src_local)
-        return self.module.run([self.src_full, dst_local])
+        self.gather(src_local)
+        return self.compute(dst_local)
