@@ -8,6 +8,8 @@
 // lengths, which keeps the row groups sharing a warp in step.
 #include <cub/device/device_radix_sort.cuh>
 
+#include <vector>
+
 #include "common.cuh"
 #include "schedule.cuh"
 
@@ -20,15 +22,6 @@ __global__ void degree_keys_kernel(const int32_t* __restrict__ indptr, int64_t n
         keys[r] = (uint32_t)(indptr[r + 1] - indptr[r]);
         rows[r] = (int32_t)r;
     }
-}
-
-// keys are sorted descending: the number of long rows is the position of the last key >= threshold
-__global__ void count_long_rows_kernel(const uint32_t* __restrict__ sorted_keys, int64_t n_rows,
-                                       uint32_t threshold, int32_t* __restrict__ n_long) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_rows) return;
-    if (sorted_keys[i] >= threshold && (i + 1 == n_rows || sorted_keys[i + 1] < threshold))
-        *n_long = (int32_t)(i + 1);
 }
 
 }  // namespace
@@ -44,8 +37,6 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
     if (n_rows > 0 && !d_indptr) return fg::fail(FG_ERR_INVALID_ARGUMENT, "d_indptr is NULL");
     if (long_row_threshold < 0)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "long_row_threshold must be >= 0 (0 = default)");
-    const uint32_t threshold =
-        long_row_threshold > 0 ? (uint32_t)long_row_threshold : fg::kLongRowThreshold;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     fg_row_schedule* sch = new fg_row_schedule();
     sch->n_rows = n_rows;
@@ -55,9 +46,7 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
     }
     uint32_t *keys_in = nullptr, *keys_out = nullptr;
     int32_t* rows_in = nullptr;
-    int32_t* d_n_long = nullptr;
-    int32_t h_n_long = 0;
-    uint32_t h_max_key = 0;
+    std::vector<uint32_t> h_keys;
     void* temp = nullptr;
     size_t temp_bytes = 0;
     int rc = FG_OK;
@@ -65,7 +54,6 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
         cudaFree(keys_in);
         cudaFree(keys_out);
         cudaFree(rows_in);
-        cudaFree(d_n_long);
         cudaFree(temp);
     };
 #define FG_TRY_OR_CLEAN(expr)                                                              \
@@ -95,17 +83,35 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
     FG_TRY_OR_CLEAN(cudaMalloc(&temp, temp_bytes ? temp_bytes : 1));
     FG_TRY_OR_CLEAN(cub::DeviceRadixSort::SortPairsDescending(
         temp, temp_bytes, keys_in, keys_out, rows_in, sch->d_order, (int)n_rows, 0, 32, s));
-    FG_TRY_OR_CLEAN(cudaMalloc(&d_n_long, sizeof(int32_t)));
-    FG_TRY_OR_CLEAN(cudaMemsetAsync(d_n_long, 0, sizeof(int32_t), s));
-    count_long_rows_kernel<<<blocks, threads, 0, s>>>(keys_out, n_rows, threshold, d_n_long);
-    FG_TRY_OR_CLEAN(cudaGetLastError());
-    FG_TRY_OR_CLEAN(cudaMemcpyAsync(&h_n_long, d_n_long, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
-    FG_TRY_OR_CLEAN(cudaMemcpyAsync(&h_max_key, keys_out, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    // the sorted nonzero counts come back once; the split statistics are computed on the host
+    h_keys.resize((size_t)n_rows);
+    FG_TRY_OR_CLEAN(cudaMemcpyAsync(h_keys.data(), keys_out, sizeof(uint32_t) * n_rows,
+                                    cudaMemcpyDeviceToHost, s));
     FG_TRY_OR_CLEAN(cudaStreamSynchronize(s));
-    sch->n_long = h_n_long;
-    sch->max_row_nnz = h_max_key;
 #undef FG_TRY_OR_CLEAN
     cleanup();
+    sch->max_row_nnz = h_keys[0];
+    sch->fixed_threshold = long_row_threshold;
+    int level = fg::kSplitLevels - 1;
+    int64_t running = 0;
+    for (int64_t i = 0; i < n_rows; ++i) {  // descending counts: thresholds are crossed downwards
+        const int64_t k = h_keys[(size_t)i];
+        while (level >= 0 && k < fg::split_threshold(level)) {
+            sch->rows_at_least[level] = i;
+            sch->nnz_at_least[level] = running;
+            --level;
+        }
+        if (long_row_threshold > 0 && k >= long_row_threshold) {
+            sch->fixed_rows = i + 1;
+            sch->fixed_nnz = running + k;
+        }
+        running += k;
+    }
+    for (; level >= 0; --level) {
+        sch->rows_at_least[level] = n_rows;
+        sch->nnz_at_least[level] = running;
+    }
+    sch->nnz = running;
     *out_schedule = sch;
     return FG_OK;
 }
@@ -118,8 +124,12 @@ int64_t fg_row_schedule_num_rows(const fg_row_schedule* schedule) {
     return schedule ? schedule->n_rows : 0;
 }
 
-int64_t fg_row_schedule_num_long_rows(const fg_row_schedule* schedule) {
-    return schedule ? schedule->n_long : 0;
+int64_t fg_row_schedule_rows_at_least(const fg_row_schedule* schedule, int64_t min_nnz) {
+    if (!schedule) return 0;
+    if (schedule->fixed_threshold > 0 && min_nnz == schedule->fixed_threshold) return schedule->fixed_rows;
+    for (int level = 0; level < fg::kSplitLevels; ++level)
+        if (fg::split_threshold(level) == min_nnz) return schedule->rows_at_least[level];
+    return -1;
 }
 
 void fg_row_schedule_destroy(fg_row_schedule* schedule) {

@@ -3,14 +3,21 @@
 #include <cstdint>
 
 namespace fg {
-// Rows with at least this many nonzeros are "long": they come first in the order and SpMM
-// runs them with the deep gather pipeline.
-constexpr uint32_t kLongRowThreshold = 1024;
+constexpr int kSplitLevels = 16;  // candidate long-row thresholds 64, 128, ..., 2^21
+inline int64_t split_threshold(int level) { return (int64_t)64 << level; }
 }  // namespace fg
 
 struct fg_row_schedule {
     int32_t* d_order = nullptr;  // row ids, nonzero count descending, ties in row order
     int64_t n_rows = 0;
-    int64_t n_long = 0;  // the first n_long entries of d_order are long rows
+    int64_t nnz = 0;
     int64_t max_row_nnz = 0;
+    // Rows with at least threshold nonzeros ("long" rows) sit at the front of d_order.  For every
+    // candidate threshold: how many rows that is and how many nonzeros they hold.
+    int64_t rows_at_least[fg::kSplitLevels] = {0};
+    int64_t nnz_at_least[fg::kSplitLevels] = {0};
+    // A caller-fixed threshold (0 = let each launch choose among the candidates).
+    int64_t fixed_threshold = 0;
+    int64_t fixed_rows = 0;
+    int64_t fixed_nnz = 0;
 };

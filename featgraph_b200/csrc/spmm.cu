@@ -23,9 +23,11 @@
 // Long rows.  A row cannot be split between workers (its sum is sequential), so the time of
 // the longest row is a floor under the whole launch: with 8 gathers in flight a 20,000-nonzero
 // row costs 2,500 dependent round trips to L2.  Rows the schedule marks as long therefore go
-// to spmm_long_rows_kernel, which keeps a ring of kDeep x 8 gathers in flight per lane (the
-// same sums, a deeper pipeline), and is launched first; the remaining rows follow in
-// spmm_rows_kernel.
+// to spmm_long_rows_kernel, which stages feature slices through a shared-memory ring filled by
+// cp.async (160 nonzeros in flight per row; the same sums, a deeper pipeline), and is launched
+// first; the remaining rows follow in spmm_rows_kernel.
+#include <cmath>
+
 #include "common.cuh"
 #include "schedule.cuh"
 
@@ -175,52 +177,59 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
 
 
 // ---------------------------------------------------------------------------------------------
-// Long rows: 8 lanes per (row, 32-float tile) unit, 128-bit gathers, and a register ring of
-// kDeep chunks of 8 gathers per lane.  Slot s of the ring holds chunk q (q % kDeep == s); when
-// chunk q has been added, the gathers of chunk q + kDeep are issued into the same slot, using
-// column ids that were fetched one ring revolution earlier, and the ids / values of chunk
-// q + 2*kDeep are requested.  The adds themselves run in storage order exactly as in
-// spmm_rows_kernel.
+// Long rows: one warp per (row, 32-float tile) unit, feature slices staged through a shared
+// memory ring filled by cp.async.
+//
+// The warp owns kRingStages slots of 32 nonzeros x 128 bytes.  Filling a slot: the lanes read 32
+// column ids / values (coalesced, requested one stage ahead), and eight cp.async instructions
+// copy the 32 slices - each instruction moves 4 slices, 8 lanes x 16 bytes per slice - straight
+// from L2 into the slot; the values go into the slot's value array.  Draining a slot: lane f
+// owns output column f of the tile and adds value[j] * slice[j][f] for j = 0..31 in storage
+// order (conflict-free 4-byte shared loads), i.e. the same strictly sequential sum as
+// spmm_rows_kernel.  With kRingStages - 1 slots in flight (5 x 4 KB) a 20,000-nonzero row waits
+// for memory a few times instead of 2,500 times.
 // ---------------------------------------------------------------------------------------------
-constexpr int kDeep = 4;
-constexpr int kLongThreads = 64;
-// Measured on B200: a dependent batch of 8 gathers in spmm_rows_kernel costs about 0.6 us under
-// load (a 20,000-nonzero row alone takes 1.5 ms), and gathers stream from L2 at about 17 TB/s.
-constexpr double kRoundTripSeconds = 0.6e-6;
-constexpr double kGatherBytesPerSecond = 17e12;
+constexpr int kRingStages = 6;
+constexpr int kRingNnz = 32;                 // nonzeros per slot
+constexpr int kLongWarps = 2;                // warps (= units) per block
+constexpr int kLongThreads = kLongWarps * 32;
+constexpr int kSlotFloats = kRingNnz * 32 + kRingNnz;  // 32 slices of 32 floats + 32 values
+constexpr int kLongSmemBytes = kLongWarps * kRingStages * kSlotFloats * 4;
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
 
-__global__ void __launch_bounds__(kLongThreads, 6) spmm_long_rows_kernel(const SpmmArgs a) {
-    constexpr int G = 8, CH = 8;
+__global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const SpmmArgs a) {
+    extern __shared__ __align__(16) float ring_smem[];
     const int lane = threadIdx.x & 31;
-    const int lig = lane & (G - 1);
-    const int64_t unit = (int64_t)blockIdx.x * (kLongThreads / G) + (threadIdx.x / G);
+    const int warp = threadIdx.x >> 5;
+    float* ring = ring_smem + warp * (kRingStages * kSlotFloats);
+
+    const int64_t unit = (int64_t)blockIdx.x * kLongWarps + warp;
     const int64_t n_units = (int64_t)a.n_sched * a.n_tiles;
-    const bool live = unit < n_units;
-    int row = 0, tile = 0;
-    if (live) {
-        tile = (int)(unit / a.n_sched);
-        row = a.order[a.order_begin + (int)(unit - (int64_t)tile * a.n_sched)];
-    }
-    const int col = tile * 32 + lig * 4;
-    const bool col_ok = live && col < a.d;
-    const float* xcol = a.x + (col_ok ? col : 0);
-    int start = 0, len = 0;
-    if (live) {
-        start = a.pos[row];
-        len = a.pos[row + 1] - start;
-    }
-    const int n_chunks = __reduce_max_sync(0xffffffffu, (len + CH - 1) / CH);
-    const int full_chunks = __reduce_min_sync(0xffffffffu, len / CH);  // chunks with no padding
+    if (unit >= n_units) return;  // whole warp
+    const int tile = (int)(unit / a.n_sched);
+    const int row = a.order[a.order_begin + (int)(unit - (int64_t)tile * a.n_sched)];
+    const int col0 = tile * 32;
+    const int start = a.pos[row];
+    const int len = a.pos[row + 1] - start;
+    const int n_stages = (len + kRingNnz - 1) / kRingNnz;
 
-    Slice<4> acc;
-    acc.zero();
-    Slice<4> ring[kDeep][CH];
-    float v_now[kDeep];   // this lane's value of the chunk sitting in the slot
-    int c_next[kDeep];    // this lane's column id / value of the chunk that enters the slot next
-    float v_next[kDeep];
+    // this lane's part in filling a slot: 16-byte piece `piece` of the slices of nonzeros
+    // sub, sub + 4, sub + 8, ... of the stage
+    const int piece = lane & 7;
+    const int sub = lane >> 3;
+    const bool piece_ok = col0 + piece * 4 < a.d;  // ragged last tile (d % 4 == 0)
+    const float* xpiece = a.x + col0 + piece * 4;
 
-    auto fetch_ids = [&](int q, int& c, float& v) {
-        const int k = q * CH + lig;
+    auto fetch_ids = [&](int stage, int& c, float& v) {  // nonzero `lane` of `stage`
+        const int k = stage * kRingNnz + lane;
         c = -1;
         v = 0.f;
         if (k < len) {
@@ -228,56 +237,124 @@ __global__ void __launch_bounds__(kLongThreads, 6) spmm_long_rows_kernel(const S
             v = a.vals[start + k];
         }
     };
-    auto issue = [&](int slot, int c_mine) {
+    auto fill = [&](int stage, int c_mine, float v_mine) {
+        float* slot = ring + (stage % kRingStages) * kSlotFloats;
+        if (stage < n_stages) {
+            slot[kRingNnz * 32 + lane] = v_mine;
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-            const int c = __shfl_sync(0xffffffffu, c_mine, j, G);
-            ring[slot][j].load(xcol + (int64_t)(c < 0 ? 0 : c) * a.d);
+            for (int i = 0; i < kRingNnz / 4; ++i) {
+                const int nz = i * 4 + sub;
+                const int c = __shfl_sync(0xffffffffu, c_mine, nz);
+                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * a.d);
+            }
         }
+        cp_async_commit();  // one group per stage, empty past the end, so the wait count is fixed
     };
 
-    // prologue: fill the ring, then request the ids of the next revolution
+    // Column ids / values are requested kIdsAhead stages before the stage is filled (they stream
+    // from DRAM), in a small register ring.
+    constexpr int kInFlight = kRingStages - 1;
+    constexpr int kIdsAhead = 4;
+    int c_ring[kIdsAhead];
+    float v_ring[kIdsAhead];
+    {
+        int c0[kInFlight];
+        float v0[kInFlight];
 #pragma unroll
-    for (int s = 0; s < kDeep; ++s) {
-        int c;
-        fetch_ids(s, c, v_now[s]);
-        if (s < n_chunks) issue(s, c);
+        for (int s = 0; s < kInFlight; ++s) fetch_ids(s, c0[s], v0[s]);
+#pragma unroll
+        for (int q = 0; q < kIdsAhead; ++q) fetch_ids(kInFlight + q, c_ring[q], v_ring[q]);
+#pragma unroll
+        for (int s = 0; s < kInFlight; ++s) fill(s, c0[s], v0[s]);
     }
-#pragma unroll
-    for (int s = 0; s < kDeep; ++s) fetch_ids(kDeep + s, c_next[s], v_next[s]);
 
-    for (int q0 = 0; q0 < n_chunks; q0 += kDeep) {
+    float acc = 0.f;
+#pragma unroll 1
+    for (int s0 = 0; s0 < n_stages; s0 += kIdsAhead) {
 #pragma unroll
-        for (int s = 0; s < kDeep; ++s) {
-            const int q = q0 + s;
-            if (q >= n_chunks) break;  // warp-uniform
-            if (q < full_chunks) {
+        for (int q = 0; q < kIdsAhead; ++q) {
+            const int s = s0 + q;
+            if (s >= n_stages) break;  // whole warp
+            fill(s + kInFlight, c_ring[q], v_ring[q]);
+            fetch_ids(s + kInFlight + kIdsAhead, c_ring[q], v_ring[q]);
+            cp_async_wait<kInFlight>();  // this lane's copies of stage s have landed ...
+            __syncwarp();                // ... and so have the other lanes'
+            const float* slot = ring + (s % kRingStages) * kSlotFloats;
+            const int cnt = min(kRingNnz, len - s * kRingNnz);
+            if (cnt == kRingNnz) {
 #pragma unroll
-                for (int j = 0; j < CH; ++j)
-                    acc.axpy(__shfl_sync(0xffffffffu, v_now[s], j, G), ring[s][j]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < CH; ++j) {
-                    Slice<4> next = acc;
-                    next.axpy(__shfl_sync(0xffffffffu, v_now[s], j, G), ring[s][j]);
-                    acc.select(q * CH + j < len, next);
+                for (int j4 = 0; j4 < kRingNnz; j4 += 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(slot + kRingNnz * 32 + j4);
+                    acc = fg::mul_then_add(acc, v.x, slot[(j4 + 0) * 32 + lane]);
+                    acc = fg::mul_then_add(acc, v.y, slot[(j4 + 1) * 32 + lane]);
+                    acc = fg::mul_then_add(acc, v.z, slot[(j4 + 2) * 32 + lane]);
+                    acc = fg::mul_then_add(acc, v.w, slot[(j4 + 3) * 32 + lane]);
                 }
+            } else {
+                for (int j = 0; j < cnt; ++j)
+                    acc = fg::mul_then_add(acc, slot[kRingNnz * 32 + j], slot[j * 32 + lane]);
             }
-            if (q + kDeep < n_chunks) issue(s, c_next[s]);
-            v_now[s] = v_next[s];
-            fetch_ids(q + 2 * kDeep, c_next[s], v_next[s]);
+            __syncwarp();  // the slot is refilled by the next iteration's fill()
         }
     }
-    if (col_ok) acc.store(a.out + (int64_t)row * a.d + col);
+    if (col0 + lane < a.d) a.out[(int64_t)row * a.d + col0 + lane] = acc;
+}
+
+// How many rows (from the front of the schedule) go to the long-row kernel for this launch.
+//
+// The two kernels trade throughput against the time of one long row.  Measured on B200 (C2
+// graph): spmm_rows_kernel streams gathers at about 17 TB/s but spends about 75 ns per nonzero
+// of a single row (8 gathers per L2 round trip), so a 20,000-nonzero row alone takes 1.5 ms;
+// spmm_long_rows_kernel streams at about 10 TB/s (every slice crosses shared memory twice) but
+// needs only about 12 ns per nonzero of a row.  Units run tile-major, so a kernel's longest rows
+// are met again in its last feature tile: its time is modelled as
+//     (1 - 1/tiles) * bytes / rate  +  max(bytes / rate / tiles, longest row's time).
+// The launch time for each candidate threshold is the long part plus the short part, and the
+// cheapest threshold wins.  A threshold fixed at schedule creation overrides the choice.  The
+// choice never affects a result bit.
+constexpr double kRowsRate = 17e12, kRowsSecPerNnz = 75e-9;
+constexpr double kRingRate = 10e12, kRingSecPerNnz = 12e-9;
+
+int64_t choose_long_rows(const fg_row_schedule& sch, int d, int short_tile) {
+    if (sch.fixed_threshold > 0) return sch.fixed_rows;
+    const double short_tiles = (d + short_tile - 1) / short_tile;
+    const double long_tiles = (d + 31) / 32;
+    const double longest = (double)sch.max_row_nnz;
+    auto part = [](double bytes, double rate, double tiles, double row_time) {
+        const double stream = bytes / rate;
+        return stream * (1.0 - 1.0 / tiles) + fmax(stream / tiles, row_time);
+    };
+    auto estimate = [&](double nnz_long, double threshold) {
+        double t = 0.0;
+        if (nnz_long > 0)
+            t += part(nnz_long * (4.0 * d + 8.0 * long_tiles), kRingRate, long_tiles, longest * kRingSecPerNnz);
+        if (sch.nnz - nnz_long > 0)
+            t += part((sch.nnz - nnz_long) * (4.0 * d + 8.0 * short_tiles), kRowsRate, short_tiles,
+                      fmin(threshold, longest) * kRowsSecPerNnz);
+        return t;
+    };
+    double best = estimate(0.0, longest);
+    int64_t best_rows = 0;
+    for (int level = 0; level < fg::kSplitLevels; ++level) {
+        if (sch.rows_at_least[level] == 0) break;
+        const double t = estimate((double)sch.nnz_at_least[level], (double)fg::split_threshold(level));
+        if (t < best) {
+            best = t;
+            best_rows = sch.rows_at_least[level];
+        }
+    }
+    return best_rows;
 }
 
 int launch_long(const SpmmArgs& a, cudaStream_t s) {
     const int64_t n_units = (int64_t)a.n_sched * a.n_tiles;
-    const int64_t units_per_block = kLongThreads / 8;
-    const int64_t blocks = (n_units + units_per_block - 1) / units_per_block;
+    const int64_t blocks = (n_units + kLongWarps - 1) / kLongWarps;
     if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
     if (blocks == 0) return FG_OK;
-    spmm_long_rows_kernel<<<(unsigned)blocks, kLongThreads, 0, s>>>(a);
+    static_assert(kLongSmemBytes <= 227 * 1024, "ring does not fit in shared memory");
+    FG_CUDA_TRY(cudaFuncSetAttribute(spmm_long_rows_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kLongSmemBytes));
+    spmm_long_rows_kernel<<<(unsigned)blocks, kLongThreads, kLongSmemBytes, s>>>(a);
     FG_CUDA_TRY(cudaGetLastError());
     return FG_OK;
 }
@@ -362,15 +439,12 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
         a.n_tiles = (d + 31) / 32;
         return launch<32, 1>(a, dds, s);
     }
-    // Long rows first, through the deep pipeline (CSR with a schedule only), when the longest
-    // row would otherwise set the run time: its estimated time in spmm_rows_kernel (one round
-    // trip to L2 per 8 nonzeros) against the whole launch's time at the SM<-L2 gather rate.
-    int64_t n_long = (schedule && !dds) ? schedule->n_long : 0;
-    if (n_long > 0) {
-        const double t_longest_row = (double)schedule->max_row_nnz / 8.0 * kRoundTripSeconds;
-        const double gathered_bytes = 4.0 * (double)nnz * d + 8.0 * (double)nnz * ((d + 63) / 64);
-        if (t_longest_row < gathered_bytes / kGatherBytesPerSecond) n_long = 0;
-    }
+    int tile = feat_tile ? feat_tile : auto_tile(n_cols, d);
+    const int cap = fg::pow2_ceil(d);
+    if (tile > cap) tile = cap;
+    if (tile < 4) tile = 4;
+    // Long rows first, through the shared-memory ring (CSR with a schedule only).
+    const int64_t n_long = (schedule && !dds) ? choose_long_rows(*schedule, d, tile) : 0;
     if (n_long > 0) {
         SpmmArgs h = a;
         h.n_sched = (int32_t)n_long;
@@ -381,10 +455,6 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
         a.n_sched = (int32_t)(n_rows - n_long);
         if (a.n_sched == 0) return FG_OK;
     }
-    int tile = feat_tile ? feat_tile : auto_tile(n_cols, d);
-    const int cap = fg::pow2_ceil(d);
-    if (tile > cap) tile = cap;
-    if (tile < 4) tile = 4;
     a.n_tiles = (d + tile - 1) / tile;
     switch (tile / 4) {
         case 1: return launch<1, 4>(a, dds, s);

@@ -2,11 +2,12 @@
 GPU (``torch.distributed``).  The reference is single-device (``tvm.gpu(0)`` is hard-wired,
 python/featgraph/module/spmm.py:218); this layer is what spreads its two ops over a node.
 
-SpMM: rank p owns rows ``[bounds[p], bounds[p+1])`` of the adjacency (column ids stay global)
-and the same rows of the feature matrix.  A call all-gathers the feature rows into every
-rank's own memory (the one exchange step the op has), then runs the single-GPU kernel on the
-local rows; the output stays sharded.  No row is ever split, so each output element is summed
-exactly as on one GPU.
+SpMM: rank p owns rows ``[bounds[p], bounds[p+1])`` of the adjacency and the same rows of the
+feature matrix.  A call all-gathers the feature rows into every rank's own memory (the one
+exchange step the op has), then runs the single-GPU kernel on the local rows; the output stays
+sharded.  No row is ever split, so each output element is summed exactly as on one GPU.
+Row blocks differ in size, so the gather runs over equal slots of a padded buffer (one plain
+all-gather) and each shard's column ids are remapped once, at construction, to point into it.
 
 SDDMM: rank p owns the edges of its rows (a contiguous range of the CSR-ordered edge list).  The
 row-side features are local, the column-side features are all-gathered; the per-edge output
@@ -58,6 +59,50 @@ def all_gather_rows(full, local, bounds, group=None):
     return full
 
 
+def padded_layout(bounds):
+    """Equal-sized slots for an all-gather of unequal row blocks: rank p's rows sit at
+    ``[p*slot, p*slot + rows_p)`` of a ``world*slot``-row buffer.  Returns ``(slot, shift)`` with
+    ``shift[p] = p*slot - bounds[p]``, the amount to add to a global row id owned by rank p."""
+    bounds = np.asarray(bounds, dtype=np.int64)
+    world = bounds.shape[0] - 1
+    slot = int(np.diff(bounds).max()) if world > 0 else 0
+    shift = np.arange(world, dtype=np.int64) * slot - bounds[:-1]
+    return slot, shift
+
+
+def remap_columns_to_padded(adj_csr, bounds):
+    """Copy of a CSR row shard whose column ids point into the padded gather buffer.  The map is
+    increasing, so the order of a row's nonzeros (and with it every sum) is unchanged."""
+    slot, shift = padded_layout(bounds)
+    world = len(shift)
+    owner = np.searchsorted(np.asarray(bounds[1:], dtype=np.int64), adj_csr.indices, side="right")
+    new_cols = (adj_csr.indices.astype(np.int64) + shift[owner]).astype(adj_csr.indices.dtype)
+    out = scipy.sparse.csr_matrix((adj_csr.data, new_cols, adj_csr.indptr), shape=(adj_csr.shape[0], world * slot))
+    return out
+
+
+def all_gather_padded(padded, local, bounds, group=None):
+    """All-gather of unequal row blocks through equal slots: ``padded[p*slot : p*slot + rows_p] =
+    rank p's local`` on every rank, as ONE equal-sized all-gather (in place: each rank first copies
+    its block into its own slot)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    slot, _ = padded_layout(bounds)
+    rows = int(bounds[rank + 1] - bounds[rank])
+    if tuple(local.shape[1:]) != tuple(padded.shape[1:]) or local.shape[0] != rows:
+        raise ValueError("local block has shape %s, rank %d owns %d rows" % (tuple(local.shape), rank, rows))
+    if padded.shape[0] != world * slot:
+        raise ValueError("padded buffer has %d rows, want %d" % (padded.shape[0], world * slot))
+    mine = padded[rank * slot:(rank + 1) * slot]
+    mine[:rows].copy_(local)
+    if world > 1:
+        if dist.get_backend(group) == "nccl":
+            dist.all_gather_into_tensor(padded, mine, group=group)
+        else:
+            dist.all_gather([padded[p * slot:(p + 1) * slot] for p in range(world)], mine.clone(), group=group)
+    return padded
+
+
 class _ShardedBase:
     def __init__(self, bounds, group, device):
         self.group = group
@@ -67,12 +112,10 @@ class _ShardedBase:
         assert self.bounds.shape[0] == self.world + 1
         self.row_lo, self.row_hi = int(self.bounds[self.rank]), int(self.bounds[self.rank + 1])
         self.device = device
+        self.slot, self.shift = padded_layout(self.bounds)
 
-    def _gather(self, full, local):
-        if not dist.is_initialized():
-            full[self.row_lo:self.row_hi].copy_(local)
-            return full
-        return all_gather_rows(full, local, self.bounds, self.group)
+    def _gather(self, padded, local):
+        return all_gather_padded(padded, local, self.bounds, self.group)
 
 
 class ShardedSpMM(_ShardedBase):
@@ -86,15 +129,16 @@ class ShardedSpMM(_ShardedBase):
         super().__init__(bounds, group, device)
         assert local_adj.shape[0] == self.row_hi - self.row_lo
         assert local_adj.shape[1] == int(self.bounds[-1]), "square adjacency expected (features are row-sharded)"
-        self.module = VanillaSpMMcuda(local_adj, device=device)
+        # the kernel gathers from the padded all-gather buffer, so its column ids are remapped once
+        self.module = VanillaSpMMcuda(remap_columns_to_padded(local_adj, self.bounds), device=device)
         self.device = self.module.ctx
-        self.n = local_adj.shape[1]
+        self.n = self.world * self.slot
         self.x_full = None
 
     def build(self, feat_len, feat_tile=0):
         from .placeholder import placeholder
         self.module.build([placeholder((self.n, feat_len))], {}, {"feat_tile": feat_tile})
-        self.x_full = torch.empty((self.n, feat_len), dtype=torch.float32, device=self.device)
+        self.x_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, x_local):
         """The exchange step alone: every rank's feature rows into this rank's ``x_full``."""
@@ -117,15 +161,15 @@ class ShardedSDDMM(_ShardedBase):
         from .module import VanillaSDDMMcuda
         super().__init__(bounds, group, device)
         assert local_adj.shape[0] == self.row_hi - self.row_lo
-        self.module = VanillaSDDMMcuda(local_adj.tocoo(), device=device)
+        self.module = VanillaSDDMMcuda(remap_columns_to_padded(local_adj, self.bounds).tocoo(), device=device)
         self.device = self.module.ctx
-        self.n = local_adj.shape[1]
+        self.n = self.world * self.slot
         self.src_full = None
 
     def build(self, feat_len):
         from .placeholder import placeholder
         self.module.build([placeholder((self.n, feat_len)), placeholder((self.row_hi - self.row_lo, feat_len))], {}, {})
-        self.src_full = torch.empty((self.n, feat_len), dtype=torch.float32, device=self.device)
+        self.src_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, src_local):
         return self._gather(self.src_full, src_local)

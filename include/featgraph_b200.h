@@ -59,17 +59,18 @@ int fg_device_info(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor, int6
  * -------------------------------------------------------------------------------------- */
 typedef struct fg_row_schedule fg_row_schedule;
 
-/* d_indptr: n_rows+1 ascending positions.  long_row_threshold: rows with at least this many
- * nonzeros are marked long (0 = the library's default; INT32_MAX = none).  Synchronises
- * `stream` before returning. */
+/* d_indptr: n_rows+1 ascending positions.  long_row_threshold: 0 = each SpMM launch decides
+ * which rows count as long (see fg_spmm_csr_f32); > 0 fixes it: rows with at least that many
+ * nonzeros always take the long-row kernel (INT32_MAX = none ever do).  Synchronises `stream`
+ * before returning. */
 int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long_row_threshold,
                            void* stream, fg_row_schedule** out_schedule);
 /* Device pointer to the n_rows row ids in visiting order (valid until destroy). */
 const int32_t* fg_row_schedule_order(const fg_row_schedule* schedule);
 int64_t fg_row_schedule_num_rows(const fg_row_schedule* schedule);
-/* How many rows at the front of the order are "long" (at or above the threshold): SpMM runs those
- * with a deeper gather pipeline so that one long sequential row does not set the run time. */
-int64_t fg_row_schedule_num_long_rows(const fg_row_schedule* schedule);
+/* Number of rows with at least min_nnz nonzeros, for min_nnz a power of two in 64..2^21 or the
+ * fixed threshold given at creation; -1 for any other value. */
+int64_t fg_row_schedule_rows_at_least(const fg_row_schedule* schedule, int64_t min_nnz);
 void fg_row_schedule_destroy(fg_row_schedule* schedule);
 
 /* --------------------------------------------------------------------------------------

@@ -46,14 +46,14 @@ def guards_intact(buf):
     return bool(torch.isnan(buf[:GUARD]).all() and torch.isnan(buf[-GUARD:]).all())
 
 
-def spmm_csr(indptr, indices, vals, x, feat_tile=0, use_schedule=True, check_guards=True):
+def spmm_csr(indptr, indices, vals, x, feat_tile=0, use_schedule=True, check_guards=True, long_row_threshold=0):
     """fg_spmm_csr_f32 on numpy inputs; returns a numpy [n_rows, d]."""
     L = _native.lib()
     n_rows = len(indptr) - 1
     n_cols, d = x.shape
     ip, ix, vv, xx = dev(indptr, np.int32), dev(indices, np.int32), dev(vals, np.float32), dev(x, np.float32)
     buf, out = guarded(n_rows * d)
-    sch = Schedule(ip, n_rows) if use_schedule else None
+    sch = Schedule(ip, n_rows, long_row_threshold) if use_schedule else None
     _native.check(L.fg_spmm_csr_f32(sch.h if sch else None, p(ip), p(ix), p(vv), p(xx), p(out), n_rows, n_cols,
                                     len(indices), d, feat_tile, stream()))
     torch.cuda.synchronize()

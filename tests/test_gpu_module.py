@@ -141,3 +141,57 @@ def test_sddmm_quirk_column_partitions_follow_row_argument(adj_coo):
         m.edge_mapping  # 1 x 1 after the overwrite: not partitioned
     m = VanillaSDDMMx86(adj_coo.copy(), 3, 1)
     assert m.edge_mapping.shape == (adj_coo.nnz,) and m.edge_mapping.dtype == np.int64
+
+
+@pytest.mark.parametrize("world", [1, 3, 8])
+def test_row_shards_on_one_gpu_reproduce_the_whole_graph(oracle, world):
+    """The per-rank work of the multi-GPU layer, run shard after shard on one GPU: remapped column ids
+    gathering from the padded buffer give the rows / edges of the single-GPU result, bit for bit (SpMM)."""
+    from featgraph_b200 import graphgen
+    from featgraph_b200.sharded import padded_layout, remap_columns_to_padded, shard_csr_rows
+    from featgraph_b200.util import nnz_balanced_row_ranges
+    n, d = 3000, 64
+    adj = graphgen.power_law_graph(n, 200_000, seed=21, kmax=2500)
+    x = graphgen.uniform_features((n, d), seed=22)
+    y = graphgen.uniform_features((n, d), seed=23)
+    bounds = nnz_balanced_row_ranges(adj.indptr, world)
+    slot, shift = padded_layout(bounds)
+    padded = np.zeros((world * slot, d), dtype=np.float32)
+    for p in range(world):
+        lo, hi = int(bounds[p]), int(bounds[p + 1])
+        padded[p * slot:p * slot + hi - lo] = x[lo:hi]
+    padded_dev = torch.from_numpy(padded).cuda()
+    want = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)
+    coo = adj.tocoo()
+    want_e = oracle.sddmm(coo.row, coo.col, x, y)
+    for p in range(world):
+        lo, hi = int(bounds[p]), int(bounds[p + 1])
+        local = remap_columns_to_padded(shard_csr_rows(adj, bounds, p), bounds)
+        m = VanillaSpMMcuda(local)
+        m.build([placeholder((world * slot, d))], {}, {})
+        np.testing.assert_array_equal(m.run([padded_dev]).cpu().numpy(), want[lo:hi])
+        s = VanillaSDDMMcuda(local.tocoo())
+        s.build([placeholder((world * slot, d)), placeholder((hi - lo, d))], {}, {})
+        got = s.run([padded_dev, torch.from_numpy(y[lo:hi].copy()).cuda()]).cpu().numpy()
+        np.testing.assert_allclose(got, want_e[adj.indptr[lo]:adj.indptr[hi]], rtol=RTOL, atol=ATOL)
+
+
+def test_sharded_wrappers_single_process(oracle):
+    """ShardedSpMM / ShardedSDDMM without a process group (world size 1)."""
+    from featgraph_b200 import graphgen
+    from featgraph_b200.sharded import ShardedSDDMM, ShardedSpMM
+    from featgraph_b200.util import nnz_balanced_row_ranges
+    n, d = 1500, 32
+    adj = graphgen.power_law_graph(n, 60_000, seed=31, kmax=900)
+    x = graphgen.uniform_features((n, d), seed=32)
+    y = graphgen.uniform_features((n, d), seed=33)
+    bounds = nnz_balanced_row_ranges(adj.indptr, 1)
+    sp_ = ShardedSpMM(adj, bounds)
+    sp_.build(d)
+    out = sp_.run(torch.from_numpy(x).cuda()).cpu().numpy()
+    np.testing.assert_array_equal(out, oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x))
+    sd = ShardedSDDMM(adj, bounds)
+    sd.build(d)
+    e = sd.run(torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()).cpu().numpy()
+    coo = adj.tocoo()
+    np.testing.assert_allclose(e, oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)

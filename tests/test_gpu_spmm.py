@@ -96,8 +96,11 @@ def test_long_rows_take_the_deep_pipeline_and_stay_exact(oracle, d):
     a.data = (np.random.default_rng(78).random(a.nnz, dtype=np.float32) * 2 - 1).astype(np.float32)
     x = graphgen.uniform_features((6000, d), seed=79 + d)
     want = oracle.spmm_csr(a.indptr, a.indices, a.data, x)
-    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x), want)
-    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x, feat_tile=32), want)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x), want)  # split chosen per launch
+    for threshold in (1, 64, 1024, 1031, 4096, 2 ** 31 - 1):
+        np.testing.assert_array_equal(
+            G.spmm_csr(a.indptr, a.indices, a.data, x, long_row_threshold=threshold), want)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x, feat_tile=32, long_row_threshold=1024), want)
     np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x, use_schedule=False), want)
 
 
@@ -106,8 +109,9 @@ def test_every_row_long(oracle):
     from featgraph_b200 import graphgen
     a = graphgen._csr_from_degrees(np.full(37, 1500, dtype=np.int64), 4000, seed=5)
     x = graphgen.uniform_features((4000, 64), seed=6)
-    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x),
-                                  oracle.spmm_csr(a.indptr, a.indices, a.data, x))
+    want = oracle.spmm_csr(a.indptr, a.indices, a.data, x)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x, long_row_threshold=1024), want)
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x), want)
 
 
 def test_unsorted_and_duplicate_columns_keep_storage_order(oracle):
@@ -160,13 +164,18 @@ def test_row_schedule_is_degree_descending_and_stable():
     order = _device.view_device_int32(addr, 5000, torch.device("cuda", torch.cuda.current_device())).cpu().numpy()
     want = np.argsort(-deg, kind="stable")
     np.testing.assert_array_equal(order, want)
-    assert _native.lib().fg_row_schedule_num_long_rows(sch.h) == 0
+    L = _native.lib()
+    assert L.fg_row_schedule_rows_at_least(sch.h, 1024) == 0
+    assert L.fg_row_schedule_rows_at_least(sch.h, 512) == 1
     sch.close()
     deg[[5, 4000, 77]] = [1024, 3000, 1023]
     indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
-    sch = G.Schedule(G.dev(indptr), 5000)
-    assert _native.lib().fg_row_schedule_num_long_rows(sch.h) == 2
-    assert _native.lib().fg_row_schedule_num_rows(sch.h) == 5000
+    sch = G.Schedule(G.dev(indptr), 5000, long_row_threshold=1000)
+    assert L.fg_row_schedule_rows_at_least(sch.h, 1024) == 2
+    assert L.fg_row_schedule_rows_at_least(sch.h, 1000) == 3
+    assert L.fg_row_schedule_rows_at_least(sch.h, 64) == int((deg >= 64).sum())
+    assert L.fg_row_schedule_rows_at_least(sch.h, 1001) == -1
+    assert L.fg_row_schedule_num_rows(sch.h) == 5000
     sch.close()
 
 

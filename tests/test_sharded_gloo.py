@@ -31,7 +31,8 @@ def _worker(rank, world, port, tmpdir):
     try:
         import oracle
         from featgraph_b200 import graphgen
-        from featgraph_b200.sharded import all_gather_rows, shard_csr_rows
+        from featgraph_b200.sharded import (all_gather_padded, all_gather_rows, padded_layout,
+                                            remap_columns_to_padded, shard_csr_rows)
         from featgraph_b200.util import nnz_balanced_row_ranges
 
         n, d = 600, 24
@@ -54,6 +55,21 @@ def _worker(rank, world, port, tmpdir):
         full = torch.full((n, d), float("nan"))
         all_gather_rows(full, torch.from_numpy(x[lo:hi].copy()), bounds)
         np.testing.assert_array_equal(full.numpy(), x)
+
+        # the same through equal slots of a padded buffer, with column ids remapped into it
+        slot, shift = padded_layout(bounds)
+        assert slot == int(np.diff(bounds).max())
+        padded = torch.zeros((world * slot, d))
+        all_gather_padded(padded, torch.from_numpy(x[lo:hi].copy()), bounds)
+        for p in range(world):
+            np.testing.assert_array_equal(padded[p * slot:p * slot + int(bounds[p + 1] - bounds[p])].numpy(),
+                                          x[int(bounds[p]):int(bounds[p + 1])])
+        remapped = remap_columns_to_padded(local, bounds)
+        assert remapped.shape == (hi - lo, world * slot) and remapped.indices.dtype == np.int32
+        np.testing.assert_array_equal(padded.numpy()[remapped.indices], x[local.indices])
+        np.testing.assert_array_equal(
+            oracle.spmm_csr(remapped.indptr, remapped.indices, remapped.data, padded.numpy()),
+            oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)[lo:hi])
 
         # per-rank SpMM on the gathered features == rows [lo, hi) of the whole product
         whole = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)
