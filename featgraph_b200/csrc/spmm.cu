@@ -27,6 +27,7 @@
 // cp.async (160 nonzeros in flight per row; the same sums, a deeper pipeline), and is launched
 // first; the remaining rows follow in spmm_rows_kernel.
 #include <cmath>
+#include <mutex>
 
 #include "common.cuh"
 #include "schedule.cuh"
@@ -487,3 +488,124 @@ int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
 }
 
 }  // extern "C"
+
+// =============================================================================================
+// SpMM without any allocation: fg_spmm_csr_f32_static
+//
+// For callers that must not see a cudaMalloc: a serving process that has handed all of the
+// device's memory to its own pool (an allocation by this library would fail or eat into that
+// pool's reserve), or a latency-critical loop where the device-wide synchronisation hidden in
+// cudaMalloc / cudaFree is not acceptable.  The regular path needs an fg_row_schedule, which
+// is built with cudaMalloc'ed buffers; here the row order is rebuilt on every call inside one
+// statically allocated device array, so the entry point only launches kernels.
+//
+// The order is a bucket order (rows grouped by floor(log2(nonzeros)), heaviest bucket first)
+// rather than a full sort: any order gives the same output bits, the grouping is what the
+// kernel needs for balance.  No long-row kernel is used on this path.
+// =============================================================================================
+namespace {
+
+constexpr int kStaticBuckets = 64;  // bucket = number of significant bits of the row's nonzero count
+// Scratch layout (int32 words): [0, FG_SPMM_STATIC_MAX_ROWS) row order,
+// then kStaticBuckets bucket sizes, then kStaticBuckets fill cursors.
+constexpr int64_t kStaticWords = (int64_t)FG_SPMM_STATIC_MAX_ROWS + 2 * kStaticBuckets;
+static __device__ __align__(256) int32_t g_spmm_static_scratch[kStaticWords];
+
+__device__ __forceinline__ int static_bucket(int nnz_in_row) { return nnz_in_row <= 0 ? 0 : 32 - __clz(nnz_in_row); }
+
+// Every call starts from zeroed counters: the array keeps whatever the previous call left.
+__global__ void static_clear_kernel(int32_t* counters) {
+    if (threadIdx.x < 2 * kStaticBuckets) counters[threadIdx.x] = 0;
+}
+
+__global__ void static_count_kernel(const int32_t* __restrict__ indptr, int32_t n_rows, int32_t* sizes) {
+    __shared__ int local[kStaticBuckets];
+    if (threadIdx.x < kStaticBuckets) local[threadIdx.x] = 0;
+    __syncthreads();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n_rows) atomicAdd(&local[static_bucket(indptr[r + 1] - indptr[r])], 1);
+    __syncthreads();
+    if (threadIdx.x < kStaticBuckets && local[threadIdx.x]) atomicAdd(&sizes[threadIdx.x], local[threadIdx.x]);
+}
+
+// cursor[b] = first slot of bucket b when buckets are laid out from the heaviest down
+__global__ void static_offsets_kernel(const int32_t* sizes, int32_t* cursors) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int at = 0;
+        for (int b = kStaticBuckets - 1; b >= 0; --b) {
+            cursors[b] = at;
+            at += sizes[b];
+        }
+    }
+}
+
+__global__ void static_scatter_kernel(const int32_t* __restrict__ indptr, int32_t n_rows, int32_t* cursors,
+                                      int32_t* __restrict__ order) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n_rows) order[atomicAdd(&cursors[static_bucket(indptr[r + 1] - indptr[r])], 1)] = r;
+}
+
+// Device address of the scratch array, looked up once per device.  In host code the array's
+// name is only a handle for the runtime; cudaGetSymbolAddress gives the pointer kernels can use.
+int static_scratch_address(int32_t** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex lock;
+    static int32_t* address[kMaxDevices] = {nullptr};
+    int dev = 0;
+    FG_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fg::fail(FG_ERR_INVALID_ARGUMENT, "device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> hold(lock);
+    if (!address[dev]) {
+        void* p = nullptr;
+        FG_CUDA_TRY(cudaGetSymbolAddress(&p, g_spmm_static_scratch));
+        if (!p) return fg::fail(FG_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        address[dev] = static_cast<int32_t*>(p);
+    }
+    *out = address[dev];
+    return FG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, const float* d_vals,
+                           const float* d_x, float* d_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                           int32_t d, int32_t feat_tile, void* stream) {
+    if (n_rows < 0) return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld", (long long)n_rows);
+    if (n_rows > FG_SPMM_STATIC_MAX_ROWS)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT,
+                        "n_rows=%lld is beyond the %d rows the static scratch array holds; use "
+                        "fg_row_schedule_create + fg_spmm_csr_f32 for larger matrices",
+                        (long long)n_rows, (int)FG_SPMM_STATIC_MAX_ROWS);
+    if (n_cols < 0 || nnz < 0 || d < 1)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_cols=%lld nnz=%lld d=%d", (long long)n_cols,
+                        (long long)nnz, d);
+    if (n_rows == 0) return FG_OK;
+    if (!d_indptr || !d_out) return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL position or output array");
+    int32_t* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != FG_OK) return rc;
+    int32_t* order = scratch;
+    int32_t* sizes = scratch + FG_SPMM_STATIC_MAX_ROWS;
+    int32_t* cursors = sizes + kStaticBuckets;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n_rows + threads - 1) / threads);
+    static_clear_kernel<<<1, 2 * kStaticBuckets, 0, s>>>(sizes);
+    static_count_kernel<<<blocks, threads, 0, s>>>(d_indptr, (int32_t)n_rows, sizes);
+    static_offsets_kernel<<<1, 32, 0, s>>>(sizes, cursors);
+    static_scatter_kernel<<<blocks, threads, 0, s>>>(d_indptr, (int32_t)n_rows, cursors, order);
+    FG_CUDA_TRY(cudaGetLastError());
+    // a schedule view over the scratch array; "fixed threshold, no rows" keeps the long-row kernel off
+    fg_row_schedule view;
+    view.d_order = order;
+    view.n_rows = n_rows;
+    view.fixed_threshold = INT32_MAX;
+    view.fixed_rows = 0;
+    return spmm_dispatch(&view, d_indptr, d_indices, d_vals, d_x, d_out, n_rows, n_cols, nnz, d, 1,
+                         feat_tile, stream, false);
+}
+
+}  // extern "C"
+

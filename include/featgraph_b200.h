@@ -104,6 +104,26 @@ int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
                     int32_t num_col_partitions, int32_t feat_tile, void* stream);
 
 /* --------------------------------------------------------------------------------------
+ * SpMM, CSR, without any device allocation (no counterpart in the reference; it exists for
+ * callers that cannot tolerate a cudaMalloc - a process whose own pool already owns all device
+ * memory, or a latency-critical loop that must not hit the device-wide synchronisation an
+ * allocation implies).  Same arguments, same result bits as fg_spmm_csr_f32, but no
+ * fg_row_schedule: the row order is rebuilt on every call inside a fixed device array that the
+ * library image carries (about 4 MB, resident on every GPU that loads the library until exit).
+ *  - At most FG_SPMM_STATIC_MAX_ROWS rows; more is refused with FG_ERR_INVALID_ARGUMENT.
+ *  - Calls no cudaMalloc, no cudaFree and no other allocating routine.  The first call on each device looks up
+ *    the array's device address (cudaGetSymbolAddress); make that first call outside any stream
+ *    capture.
+ *  - All calls on a device share the one array (its counters are cleared at the start of each
+ *    call): two calls that overlap on the GPU - different streams, no ordering between them -
+ *    race on it.  Calls on one stream are safe.
+ * -------------------------------------------------------------------------------------- */
+#define FG_SPMM_STATIC_MAX_ROWS 1048576
+int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, const float* d_vals,
+                           const float* d_x, float* d_out, int64_t n_rows, int64_t n_cols,
+                           int64_t nnz, int32_t d, int32_t feat_tile, void* stream);
+
+/* --------------------------------------------------------------------------------------
  * SDDMM, COO:  out[e] = sum_k src[col[e], k] * dst[row[e], k]
  * (src is indexed by the COLUMN id, dst by the ROW id: python/featgraph/op/vanilla_sddmm.py:47).
  * Replaces the function built from vanilla_sddmm (op/vanilla_sddmm.py:6-63) and called at
