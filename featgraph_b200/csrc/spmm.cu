@@ -24,7 +24,7 @@
 // the longest row is a floor under the whole launch: with 8 gathers in flight a 20,000-nonzero
 // row costs 2,500 dependent round trips to L2.  Rows the schedule marks as long therefore go
 // to spmm_long_rows_kernel, which stages feature slices through a shared-memory ring filled by
-// cp.async (160 nonzeros in flight per row; the same sums, a deeper pipeline), and is launched
+// cp.async (64 nonzeros in flight per row; the same sums, a deeper pipeline), and is launched
 // first; the remaining rows follow in spmm_rows_kernel.
 #include <cmath>
 #include <mutex>
@@ -187,12 +187,14 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
 // from L2 into the slot; the values go into the slot's value array.  Draining a slot: lane f
 // owns output column f of the tile and adds value[j] * slice[j][f] for j = 0..31 in storage
 // order (conflict-free 4-byte shared loads), i.e. the same strictly sequential sum as
-// spmm_rows_kernel.  With kRingStages - 1 slots in flight (5 x 4 KB) a 20,000-nonzero row waits
-// for memory a few times instead of 2,500 times.
+// spmm_rows_kernel.  A row streams through the ring with kRingStages - 1 slots (2 x 4 KB) in
+// flight and pays the memory latency once instead of once per 8 nonzeros.  Three slots (12.7 KB
+// per warp, 16 resident warps per SM) measured faster than deeper rings with fewer warps: the
+// per-lane add chain needs the other warps to fill its 4-cycle gaps.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRingStages = 6;
+constexpr int kRingStages = 3;
 constexpr int kRingNnz = 32;                 // nonzeros per slot
-constexpr int kLongWarps = 2;                // warps (= units) per block
+constexpr int kLongWarps = 4;                // warps (= units) per block
 constexpr int kLongThreads = kLongWarps * 32;
 constexpr int kSlotFloats = kRingNnz * 32 + kRingNnz;  // 32 slices of 32 floats + 32 values
 constexpr int kLongSmemBytes = kLongWarps * kRingStages * kSlotFloats * 4;
@@ -306,15 +308,15 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
 // The two kernels trade throughput against the time of one long row.  Measured on B200 (C2
 // graph): spmm_rows_kernel streams gathers at about 17 TB/s but spends about 75 ns per nonzero
 // of a single row (8 gathers per L2 round trip), so a 20,000-nonzero row alone takes 1.5 ms;
-// spmm_long_rows_kernel streams at about 10 TB/s (every slice crosses shared memory twice) but
-// needs only about 12 ns per nonzero of a row.  Units run tile-major, so a kernel's longest rows
+// spmm_long_rows_kernel streams at about 13 TB/s (every slice crosses shared memory twice) but
+// needs only about 15 ns per nonzero of a row.  Units run tile-major, so a kernel's longest rows
 // are met again in its last feature tile: its time is modelled as
 //     (1 - 1/tiles) * bytes / rate  +  max(bytes / rate / tiles, longest row's time).
 // The launch time for each candidate threshold is the long part plus the short part, and the
 // cheapest threshold wins.  A threshold fixed at schedule creation overrides the choice.  The
 // choice never affects a result bit.
 constexpr double kRowsRate = 17e12, kRowsSecPerNnz = 75e-9;
-constexpr double kRingRate = 10e12, kRingSecPerNnz = 12e-9;
+constexpr double kRingRate = 13e12, kRingSecPerNnz = 15e-9;
 
 int64_t choose_long_rows(const fg_row_schedule& sch, int d, int short_tile) {
     if (sch.fixed_threshold > 0) return sch.fixed_rows;
