@@ -318,6 +318,7 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     records = []
+    launches_before = _native.lib().fg_kernel_launch_count()
     t_start = torch.cuda.Event(enable_timing=True)
     t_stop = torch.cuda.Event(enable_timing=True)
     barrier()
@@ -325,6 +326,7 @@ def run_ours(args):
     for _ in range(args.steps):
         step(records)
     t_stop.record(stream)
+    launches = int(_native.lib().fg_kernel_launch_count() - launches_before)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_start.elapsed_time(t_stop)
@@ -408,7 +410,8 @@ def run_ours(args):
         return
     dom = max(kernels, key=lambda k: k["ms"])
     roofline = {
-        "bound": "hbm", "kernel": "%s d=%d" % (dom["op"], dom["d"]),
+        "bound": "hbm", "kernel": "%s d=%d (one library call; SDDMM at d>=256 is one launch per 64-float tile)"
+        % (dom["op"], dom["d"]),
         "achieved": dom["touched_gbs"], "peak": peak, "unit": "GB/s", "frac": dom["frac_touched"],
         "peak_kind": "of " + peak_kind, "traffic": NCU_TRAFFIC_BYTES.get((dom["op"], dom["d"])),
         "compulsory_frac": dom["frac_compulsory"],
@@ -429,7 +432,7 @@ def run_ours(args):
                                 "and feature matrices between repeats of any one)" % (8.0 * nnz / 1e6),
                    "feat_tile": args.feat_tile or "auto"},
         "roofline": roofline, "kernels": kernels, "e2e": e2e,
-        "gpu_launches": args.steps * 2 * len(dims), "clocks": clocks,
+        "gpu_launches": launches, "clocks": clocks,
     }
     if not args.no_cpu_baseline and world == 1:
         t0 = time.time()
@@ -448,7 +451,12 @@ def run_ours(args):
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; keyed by (op, feature length).  Absent = not captured.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    ("spmm", 512): 17.82e9,   # spmm_rows_kernel<16,4,0>, one launch (8 tiles inside)
+    ("spmm", 128): 4.72e9,
+    ("sddmm", 512): 25.9e9,   # sddmm_tile_kernel<16,1,8,1,0>: 8 tile launches of 3.24 GB each
+    ("sddmm", 128): 21.83e9,  # sddmm_tile_kernel<32,1,8,1,0>, single pass
+}
 
 
 def _install_build_cache(spmm, sddmm):

@@ -22,6 +22,9 @@ int fail(int code, const char* fmt, ...);
                               cudaGetErrorString(fg_err__), __FILE__, __LINE__);           \
     } while (0)
 
+// Kernels launched by this library in this process (fg_kernel_launch_count).
+void count_launches(int n);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int pow2_floor(int v) {

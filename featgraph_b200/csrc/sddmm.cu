@@ -7,9 +7,10 @@
 // store.  In between, groups of G lanes each take G consecutive edges of the 32.  For one
 // edge the group's lanes gather a slice of src[col[e]] with 128-bit loads (consecutive lanes,
 // consecutive 16 bytes) and multiply-accumulate it against the matching slice of dst[row[e]];
-// each lane ends up with G partial sums (one per edge), and a transposed butterfly - G-1
-// shuffles for G edges instead of log2(G) per edge - leaves lane i of the group holding the
-// finished dot product of edge i, which is exactly the layout of the coalesced store.
+// each lane ends up with one partial sum per edge, and a transposed butterfly - G-1 shuffles
+// for G edges instead of log2(G) per edge, its first steps done chunk by chunk so that only a
+// few partial sums are ever live - leaves lane i of the group holding the finished dot product
+// of edge i, which is exactly the layout of the coalesced store.
 //
 // Row side.  When the edge list is row-sorted (CSR order) the row-side slice stays in
 // registers while consecutive edges share the row (a ballot marks where rows change), so it is
@@ -55,7 +56,7 @@ struct SddmmArgs {
 // CACHE_DST: edge list is row-sorted, keep the row-side slice in registers.
 // MASKED: the tile is narrower than 4*G*NV floats (ragged last tile).
 template <int G, int NV, int U, bool CACHE_DST, bool MASKED>
-__global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs a) {
+__global__ void __launch_bounds__(kThreads, (NV >= 3 || (NV == 2 && !CACHE_DST)) ? 3 : 4) sddmm_tile_kernel(const SddmmArgs a) {
     static_assert(G % U == 0, "U must divide G");
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
@@ -103,20 +104,21 @@ __global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs
             change = __ballot_sync(0xffffffffu, lig == 0 || r_prev != r_l);
         }
 
-        float p[G];
+        float r[G / U];  // one partly reduced value per chunk of U edges
         float4 dcache[NV];
 #pragma unroll
         for (int i = 0; i < NV; ++i) dcache[i] = zero4;
 
 #pragma unroll
         for (int s = 0; s < G; s += U) {
-            int c[U], r[U];
+            int c[U], rr[U];
+            float pc[U];
             float4 xs[U][NV];
             float4 xd[U][NV];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 c[u] = __shfl_sync(0xffffffffu, c_l, gbase + s + u);
-                if (!CACHE_DST) r[u] = __shfl_sync(0xffffffffu, r_l, gbase + s + u);
+                if (!CACHE_DST) rr[u] = __shfl_sync(0xffffffffu, r_l, gbase + s + u);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -127,7 +129,7 @@ __global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs
                     if (MASKED && !ok[i]) xs[u][i] = zero4;
                 }
                 if (!CACHE_DST) {
-                    const float* pd = a.dst + (int64_t)r[u] * a.d;
+                    const float* pd = a.dst + (int64_t)rr[u] * a.d;
 #pragma unroll
                     for (int i = 0; i < NV; ++i) xd[u][i] = fg::ldg4(pd + colv[i]);
                 }
@@ -137,8 +139,8 @@ __global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs
                 float acc = 0.f;
                 if (CACHE_DST) {
                     if ((change >> (gbase + s + u)) & 1u) {  // uniform within the group
-                        const int rr = __shfl_sync(gmask, r_l, gbase + s + u);
-                        const float* pd = a.dst + (int64_t)rr * a.d;
+                        const int rnew = __shfl_sync(gmask, r_l, gbase + s + u);
+                        const float* pd = a.dst + (int64_t)rnew * a.d;
 #pragma unroll
                         for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
                     }
@@ -148,22 +150,37 @@ __global__ void __launch_bounds__(kThreads, 3) sddmm_tile_kernel(const SddmmArgs
 #pragma unroll
                     for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], xd[u][i]);
                 }
-                p[s + u] = acc;
+                pc[u] = acc;
             }
+            // first log2(U) steps of the transposed butterfly, inside the chunk: afterwards pc[0] on a
+            // lane holds, for the chunk's edge picked by the lane's low bits, the sum over the 2^k
+            // lanes that differ from it in those bits
+#pragma unroll
+            for (int off = 1; off < U; off <<= 1) {
+                const bool upper = (lig & off) != 0;
+#pragma unroll
+                for (int i = 0; i < U / (2 * off); ++i) {
+                    const float send = upper ? pc[2 * i] : pc[2 * i + 1];
+                    const float keep = upper ? pc[2 * i + 1] : pc[2 * i];
+                    pc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            r[s / U] = pc[0];
         }
 
-        // transposed butterfly: afterwards p[0] on lane i of the group is edge i's total
+        // remaining steps across the chunks: afterwards r[0] on lane i of the group is edge i's total
 #pragma unroll
-        for (int off = G / 2; off >= 1; off >>= 1) {
+        for (int off = U; off < G; off <<= 1) {
             const bool upper = (lig & off) != 0;
+            const int h = off / U;
 #pragma unroll
-            for (int i = 0; i < off; ++i) {
-                const float send = upper ? p[i] : p[i + off];
-                const float keep = upper ? p[i + off] : p[i];
-                p[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            for (int i = 0; i < G / U / (2 * h); ++i) {
+                const float send = upper ? r[2 * i] : r[2 * i + 1];
+                const float keep = upper ? r[2 * i + 1] : r[2 * i];
+                r[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
             }
         }
-        if (valid) a.out[e] = prev + p[0];
+        if (valid) a.out[e] = prev + r[0];
     }
 }
 
@@ -217,6 +234,7 @@ int launch_tile(const SddmmArgs& a, bool cache_dst, bool masked, unsigned blocks
             sddmm_tile_kernel<G, NV, UH, false, false><<<blocks, kThreads, 0, s>>>(a);
     }
     FG_CUDA_TRY(cudaGetLastError());
+    fg::count_launches(1);
     return FG_OK;
 }
 
@@ -277,6 +295,7 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
     if (!vec) {
         sddmm_generic_kernel<<<blocks, kThreads, 0, s>>>(d_row, d_col, d_src, d_dst, d_out, nnz, d);
         FG_CUDA_TRY(cudaGetLastError());
+        fg::count_launches(1);
         return FG_OK;
     }
     // Tile width: the whole row if the column-side matrix fits the resident share of L2 (or if

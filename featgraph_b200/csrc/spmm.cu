@@ -359,6 +359,7 @@ int launch_long(const SpmmArgs& a, cudaStream_t s) {
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kLongSmemBytes));
     spmm_long_rows_kernel<<<(unsigned)blocks, kLongThreads, kLongSmemBytes, s>>>(a);
     FG_CUDA_TRY(cudaGetLastError());
+    fg::count_launches(1);
     return FG_OK;
 }
 
@@ -374,6 +375,7 @@ int launch(const SpmmArgs& a, bool dds, cudaStream_t s) {
     else
         spmm_rows_kernel<G, VEC, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
     FG_CUDA_TRY(cudaGetLastError());
+    fg::count_launches(1);
     return FG_OK;
 }
 
@@ -599,6 +601,7 @@ int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, co
     static_offsets_kernel<<<1, 32, 0, s>>>(sizes, cursors);
     static_scatter_kernel<<<blocks, threads, 0, s>>>(d_indptr, (int32_t)n_rows, cursors, order);
     FG_CUDA_TRY(cudaGetLastError());
+    fg::count_launches(4);
     // a schedule view over the scratch array; "fixed threshold, no rows" keeps the long-row kernel off
     fg_row_schedule view;
     view.d_order = order;

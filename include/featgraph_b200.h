@@ -46,6 +46,11 @@ int fg_version(void);
 /* Text of the last error raised on the calling thread ("" if none). Never NULL. */
 const char* fg_last_error(void);
 
+/* How many SpMM / SDDMM kernels this library has launched in this process so far (the
+ * reference's timer counts calls of the built function, module/spmm.py:179; this counts the
+ * launches behind them). */
+int64_t fg_kernel_launch_count(void);
+
 /* Number of SMs, compute capability and L2 size of the current device.
  * Replaces the reference's device handle query (tvm.gpu(0), module/spmm.py:218). */
 int fg_device_info(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor, int64_t* l2_bytes);
