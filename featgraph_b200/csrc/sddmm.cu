@@ -47,7 +47,8 @@ struct SddmmArgs {
     const float* dst;  // already offset to the tile's first column
     float* out;
     int64_t nnz;
-    int32_t d;      // row stride of src / dst in floats
+    int64_t ld_src;  // row strides in floats
+    int64_t ld_dst;
     int32_t width;  // columns in this tile (<= 4*G*NV)
     int32_t accumulate;
 };
@@ -122,14 +123,14 @@ __global__ void __launch_bounds__(kThreads, (NV >= 3 || (NV == 2 && !CACHE_DST))
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const float* ps = a.src + (int64_t)c[u] * a.d;
+                const float* ps = a.src + (int64_t)c[u] * a.ld_src;
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
                     xs[u][i] = fg::ldg4(ps + colv[i]);
                     if (MASKED && !ok[i]) xs[u][i] = zero4;
                 }
                 if (!CACHE_DST) {
-                    const float* pd = a.dst + (int64_t)rr[u] * a.d;
+                    const float* pd = a.dst + (int64_t)rr[u] * a.ld_dst;
 #pragma unroll
                     for (int i = 0; i < NV; ++i) xd[u][i] = fg::ldg4(pd + colv[i]);
                 }
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(kThreads, (NV >= 3 || (NV == 2 && !CACHE_DST))
                 if (CACHE_DST) {
                     if ((change >> (gbase + s + u)) & 1u) {  // uniform within the group
                         const int rnew = __shfl_sync(gmask, r_l, gbase + s + u);
-                        const float* pd = a.dst + (int64_t)rnew * a.d;
+                        const float* pd = a.dst + (int64_t)rnew * a.ld_dst;
 #pragma unroll
                         for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
                     }
@@ -187,8 +188,8 @@ __global__ void __launch_bounds__(kThreads, (NV >= 3 || (NV == 2 && !CACHE_DST))
 // Any d, any alignment: a warp per 32 edges, lanes stride over the feature columns.
 __global__ void __launch_bounds__(kThreads, 4)
 sddmm_generic_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ col,
-                     const float* __restrict__ src, const float* __restrict__ dst,
-                     float* __restrict__ out, int64_t nnz, int32_t d) {
+                     const float* __restrict__ src, int64_t ld_src, const float* __restrict__ dst,
+                     int64_t ld_dst, float* __restrict__ out, int64_t nnz, int32_t d, int32_t accumulate) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
     for (int b = 0; b < kBatchesPerWarp; ++b) {
@@ -205,15 +206,15 @@ sddmm_generic_kernel(const int32_t* __restrict__ row, const int32_t* __restrict_
             const int r = __shfl_sync(0xffffffffu, r_l, s);
             const int c = __shfl_sync(0xffffffffu, c_l, s);
             if (r < 0) break;  // warp-uniform: the tail of the last batch
-            const float* ps = src + (int64_t)c * d;
-            const float* pd = dst + (int64_t)r * d;
+            const float* ps = src + (int64_t)c * ld_src;
+            const float* pd = dst + (int64_t)r * ld_dst;
             float p = 0.f;
             for (int k = lane; k < d; k += 32) p = fmaf(__ldg(ps + k), __ldg(pd + k), p);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) p += __shfl_xor_sync(0xffffffffu, p, off);
             if (lane == s) res = p;
         }
-        if (e < nnz) out[e] = res;
+        if (e < nnz) out[e] = accumulate ? out[e] + res : res;
     }
 }
 
@@ -271,9 +272,10 @@ int64_t l2_size_bytes() {
 
 extern "C" {
 
-int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src,
-                     const float* d_dst, float* d_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
-                     int32_t d, int32_t rows_sorted, int32_t feat_tile, void* stream) {
+int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src, int64_t ld_src,
+                     const float* d_dst, int64_t ld_dst, float* d_out, int64_t n_rows, int64_t n_cols,
+                     int64_t nnz, int32_t d, int32_t rows_sorted, int32_t accumulate, int32_t feat_tile,
+                     void* stream) {
     if (n_rows < 0 || n_cols < 0 || nnz < 0 || d < 1)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d",
                         (long long)n_rows, (long long)n_cols, (long long)nnz, d);
@@ -282,6 +284,11 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
     if (feat_tile != 0 && (feat_tile < 4 || feat_tile > 512 || (feat_tile & (feat_tile - 1))))
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "feat_tile=%d: want 0 or a power of two in 4..512",
                         feat_tile);
+    if (ld_src == 0) ld_src = d;
+    if (ld_dst == 0) ld_dst = d;
+    if (ld_src < d || ld_dst < d)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row strides ld_src=%lld ld_dst=%lld must be 0 or >= d=%d",
+                        (long long)ld_src, (long long)ld_dst, d);
     if (nnz == 0) return FG_OK;
     if (!d_row || !d_col || !d_src || !d_dst || !d_out)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL array argument");
@@ -291,9 +298,11 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
     if (nblocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
     const unsigned blocks = (unsigned)nblocks;
     const bool cache = rows_sorted != 0;
-    const bool vec = (d % 4 == 0) && fg::aligned16(d_src) && fg::aligned16(d_dst);
+    const bool vec = (d % 4 == 0) && (ld_src % 4 == 0) && (ld_dst % 4 == 0) && fg::aligned16(d_src) &&
+                     fg::aligned16(d_dst);
     if (!vec) {
-        sddmm_generic_kernel<<<blocks, kThreads, 0, s>>>(d_row, d_col, d_src, d_dst, d_out, nnz, d);
+        sddmm_generic_kernel<<<blocks, kThreads, 0, s>>>(d_row, d_col, d_src, ld_src, d_dst, ld_dst, d_out, nnz,
+                                                          d, accumulate);
         FG_CUDA_TRY(cudaGetLastError());
         fg::count_launches(1);
         return FG_OK;
@@ -319,12 +328,13 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
     a.col = d_col;
     a.out = d_out;
     a.nnz = nnz;
-    a.d = d;
+    a.ld_src = ld_src;
+    a.ld_dst = ld_dst;
     for (int f0 = 0; f0 < d; f0 += tile) {
         a.src = d_src + f0;
         a.dst = d_dst + f0;
         a.width = (d - f0 < tile) ? d - f0 : tile;
-        a.accumulate = f0 > 0;
+        a.accumulate = (f0 > 0) || accumulate;
         const int rc = launch_width(a, cache, blocks, s);
         if (rc != FG_OK) return rc;
     }

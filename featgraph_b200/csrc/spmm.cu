@@ -46,7 +46,9 @@ struct SpmmArgs {
     int32_t order_begin;   // this launch covers order[order_begin, order_begin + n_sched)
     int32_t n_sched;
     int32_t n_rows;
-    int32_t d;
+    int32_t d;        // feature columns computed by this launch
+    int64_t ldx;      // row stride of x in floats (>= d)
+    int64_t ldo;      // row stride of out in floats (>= d)
     int32_t n_tiles;
     int32_t parts;          // 1 for CSR
     int32_t cols_per_part;  // DDS only
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
                 // CH gathers are in flight before the first dependent add.
 #pragma unroll
                 for (int j = 0; j < CH; ++j)
-                    xr[j].load(xcol + (col_base + (c[j] < 0 ? 0 : c[j])) * a.d);
+                    xr[j].load(xcol + (col_base + (c[j] < 0 ? 0 : c[j])) * a.ldx);
                 // Branch-free commit: a branch here would let the compiler sink each load
                 // next to its use and serialise the gathers.
 #pragma unroll
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
         else
             total = acc;
     }
-    if (col_ok) total.store(a.out + (int64_t)row * a.d + col);
+    if (col_ok) total.store(a.out + (int64_t)row * a.ldo + col);
 }
 
 
@@ -248,7 +250,7 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
             for (int i = 0; i < kRingNnz / 4; ++i) {
                 const int nz = i * 4 + sub;
                 const int c = __shfl_sync(0xffffffffu, c_mine, nz);
-                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * a.d);
+                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * a.ldx);
             }
         }
         cp_async_commit();  // one group per stage, empty past the end, so the wait count is fixed
@@ -300,7 +302,7 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
             __syncwarp();  // the slot is refilled by the next iteration's fill()
         }
     }
-    if (col0 + lane < a.d) a.out[(int64_t)row * a.d + col0 + lane] = acc;
+    if (col0 + lane < a.d) a.out[(int64_t)row * a.ldo + col0 + lane] = acc;
 }
 
 // How many rows (from the front of the schedule) go to the long-row kernel for this launch.
@@ -403,15 +405,20 @@ int auto_tile(int64_t n_cols, int d) {
 }
 
 int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int32_t* idx,
-                  const float* vals, const float* x, float* out, int64_t n_rows, int64_t n_cols,
-                  int64_t nnz, int32_t d, int32_t parts, int32_t feat_tile, void* stream,
-                  bool dds) {
+                  const float* vals, const float* x, int64_t ldx, float* out, int64_t ldo,
+                  int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d, int32_t parts,
+                  int32_t feat_tile, void* stream, bool dds) {
     if (n_rows < 0 || n_cols < 0 || nnz < 0 || d < 1)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d",
                         (long long)n_rows, (long long)n_cols, (long long)nnz, d);
     if (n_rows > INT32_MAX || n_cols > INT32_MAX || nnz > INT32_MAX)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "sizes beyond int32 indexing are not supported");
     if (parts < 1) return fg::fail(FG_ERR_INVALID_ARGUMENT, "num_col_partitions must be >= 1");
+    if (ldx == 0) ldx = d;
+    if (ldo == 0) ldo = d;
+    if (ldx < d || ldo < d)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row strides ldx=%lld ldo=%lld must be 0 or >= d=%d",
+                        (long long)ldx, (long long)ldo, d);
     if (feat_tile != 0 && (feat_tile < 4 || feat_tile > 128 || (feat_tile & (feat_tile - 1))))
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "feat_tile=%d: want 0 or a power of two in 4..128",
                         feat_tile);
@@ -434,11 +441,13 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     a.n_sched = (int32_t)n_rows;
     a.n_rows = (int32_t)n_rows;
     a.d = d;
+    a.ldx = ldx;
+    a.ldo = ldo;
     a.parts = parts;
     a.cols_per_part = dds ? (int32_t)((n_cols + parts - 1) / parts) : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    const bool vec = (d % 4 == 0) && fg::aligned16(x) && fg::aligned16(out);
+    const bool vec = (d % 4 == 0) && (ldx % 4 == 0) && (ldo % 4 == 0) && fg::aligned16(x) && fg::aligned16(out);
     if (!vec) {
         // scalar path: 32 lanes x 1 float per unit
         a.n_tiles = (d + 31) / 32;
@@ -476,19 +485,19 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
 extern "C" {
 
 int fg_spmm_csr_f32(const fg_row_schedule* schedule, const int32_t* d_indptr,
-                    const int32_t* d_indices, const float* d_vals, const float* d_x, float* d_out,
-                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d, int32_t feat_tile,
-                    void* stream) {
-    return spmm_dispatch(schedule, d_indptr, d_indices, d_vals, d_x, d_out, n_rows, n_cols, nnz, d,
-                         1, feat_tile, stream, false);
+                    const int32_t* d_indices, const float* d_vals, const float* d_x, int64_t ldx,
+                    float* d_out, int64_t ldo, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                    int32_t feat_tile, void* stream) {
+    return spmm_dispatch(schedule, d_indptr, d_indices, d_vals, d_x, ldx, d_out, ldo, n_rows, n_cols,
+                         nnz, d, 1, feat_tile, stream, false);
 }
 
 int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
-                    const int32_t* d_s1_idx, const float* d_vals, const float* d_x, float* d_out,
-                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                    const int32_t* d_s1_idx, const float* d_vals, const float* d_x, int64_t ldx,
+                    float* d_out, int64_t ldo, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
                     int32_t num_col_partitions, int32_t feat_tile, void* stream) {
-    return spmm_dispatch(schedule, d_s1_pos, d_s1_idx, d_vals, d_x, d_out, n_rows, n_cols, nnz, d,
-                         num_col_partitions, feat_tile, stream, true);
+    return spmm_dispatch(schedule, d_s1_pos, d_s1_idx, d_vals, d_x, ldx, d_out, ldo, n_rows, n_cols,
+                         nnz, d, num_col_partitions, feat_tile, stream, true);
 }
 
 }  // extern "C"
@@ -608,8 +617,8 @@ int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, co
     view.n_rows = n_rows;
     view.fixed_threshold = INT32_MAX;
     view.fixed_rows = 0;
-    return spmm_dispatch(&view, d_indptr, d_indices, d_vals, d_x, d_out, n_rows, n_cols, nnz, d, 1,
-                         feat_tile, stream, false);
+    return spmm_dispatch(&view, d_indptr, d_indices, d_vals, d_x, d, d_out, d, n_rows, n_cols, nnz, d,
+                         1, feat_tile, stream, false);
 }
 
 }  // extern "C"

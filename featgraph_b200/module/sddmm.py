@@ -53,6 +53,7 @@ class SDDMMbase:
         self._rows_sorted = int(sorted_flag.value)
         self._shapes = None
         self._feat_tile = 0
+        self._staging = None
         self.out = None
 
     def _register(self):
@@ -117,9 +118,9 @@ class SDDMMbase:
     def _launch(self, src, dst, out):
         d = self._shapes[0][1]
         dev.check(dev.lib().fg_sddmm_coo_f32(dev.ptr(self._adj_row), dev.ptr(self._adj_col),
-                                             dev.ptr(src), dev.ptr(dst), dev.ptr(out),
+                                             dev.ptr(src), 0, dev.ptr(dst), 0, dev.ptr(out),
                                              self._num_rows, self._num_cols, self._nnz, d,
-                                             self._rows_sorted, self._feat_tile,
+                                             self._rows_sorted, 0, self._feat_tile,
                                              dev.stream_ptr(self._device)))
 
     def run(self, inputs):
@@ -134,17 +135,33 @@ class SDDMMbase:
             self._launch(src, dst, self.out)
         return self.out
 
-    def run_host(self, inputs, out=None):
-        """Host-buffer call: features host->device, kernel, result device->host, wait."""
+    def run_host(self, inputs, out=None, chunk=0):
+        """Host-buffer call: both feature matrices in host memory (numpy or CPU tensors, float32,
+        contiguous; pinned for full copy speed), per-edge result back in host memory, copies
+        pipelined against the kernels by ``fg_sddmm_coo_f32_host``.  Returns the host tensor."""
+        if self.out is None:
+            raise RuntimeError("call build() before run_host()")
         ts = [torch.from_numpy(x) if isinstance(x, np.ndarray) else x for x in inputs]
+        for t, shape in zip(ts, self._shapes):
+            if t.device.type != "cpu" or t.dtype != torch.float32 or not t.is_contiguous() \
+                    or tuple(t.shape) != tuple(shape):
+                raise ValueError("run_host wants contiguous float32 host arrays of shapes %s" % (self._shapes,))
+        if out is None:
+            out = torch.empty((self._nnz,), dtype=torch.float32).pin_memory()
+        if out.device.type != "cpu" or out.dtype != torch.float32 or tuple(out.shape) != (self._nnz,):
+            raise ValueError("out must be a float32 host tensor of shape (%d,)" % self._nnz)
+        import ctypes
+        d = self._shapes[0][1]
         with torch.cuda.device(self._device):
-            ds = [t.to(self._device, non_blocking=True) for t in ts]
-            res = self.run(ds)
-            if out is None:
-                return res.cpu()
-            out.copy_(res, non_blocking=True)
-            torch.cuda.current_stream(self._device).synchronize()
-            return out
+            if self._staging is None or tuple(self._staging[0].shape) != tuple(self._shapes[0]):
+                self._staging = (torch.empty(self._shapes[0], dtype=torch.float32, device=self._device),
+                                 torch.empty(self._shapes[1], dtype=torch.float32, device=self._device))
+            dev.check(dev.lib().fg_sddmm_coo_f32_host(
+                dev.ptr(self._adj_row), dev.ptr(self._adj_col), ctypes.c_void_p(ts[0].data_ptr()),
+                ctypes.c_void_p(ts[1].data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(self._staging[0]),
+                dev.ptr(self._staging[1]), dev.ptr(self.out), self._num_rows, self._num_cols, self._nnz, d,
+                self._rows_sorted, int(chunk), dev.stream_ptr(self._device)))
+        return out
 
     def measure_average_time(self, inputs, num_runs):
         """Mean seconds per call over ``num_runs`` back-to-back calls (reference :131-150)."""

@@ -63,6 +63,7 @@ class SpMMbase:
                 self._adj_vals = dev.upload(adj_csr.data, self._device)
         self._feat_shape = None
         self._feat_tile = 0
+        self._x_staging = None
         self.out = None
 
     def __del__(self):
@@ -134,12 +135,12 @@ class SpMMbase:
         s = dev.stream_ptr(self._device)
         if self._num_col_partitions > 1:
             rc = L.fg_spmm_dds_f32(self._schedule, dev.ptr(self._adj_pos), dev.ptr(self._adj_idx),
-                                   dev.ptr(self._adj_vals), dev.ptr(x), dev.ptr(out),
+                                   dev.ptr(self._adj_vals), dev.ptr(x), 0, dev.ptr(out), 0,
                                    self._num_rows, self._num_cols, self._nnz, d,
                                    self._num_col_partitions, self._feat_tile, s)
         else:
             rc = L.fg_spmm_csr_f32(self._schedule, dev.ptr(self._adj_pos), dev.ptr(self._adj_idx),
-                                   dev.ptr(self._adj_vals), dev.ptr(x), dev.ptr(out),
+                                   dev.ptr(self._adj_vals), dev.ptr(x), 0, dev.ptr(out), 0,
                                    self._num_rows, self._num_cols, self._nnz, d,
                                    self._feat_tile, s)
         dev.check(rc)
@@ -155,20 +156,37 @@ class SpMMbase:
             self._launch(x, self.out)
         return self.out
 
-    def run_host(self, inputs, out=None):
-        """Host-buffer call: copy the (numpy or CPU-tensor) features to the device, run,
-        copy the result back and wait.  Pinned buffers are used as given; pageable ones
-        are staged by the driver."""
+    def run_host(self, inputs, out=None, chunk=0):
+        """Host-buffer call: features in host memory (numpy array or CPU tensor, float32,
+        contiguous; pinned memory gives full copy speed), result back in host memory.  Copies and
+        kernels are pipelined over column windows by ``fg_spmm_csr_f32_host``.  ``out``: a CPU
+        float32 tensor ``[num_rows, feat_len]`` to fill (allocated pinned if omitted).  Returns it."""
+        if self.out is None:
+            raise RuntimeError("call build() before run_host()")
         (x,) = inputs
         xt = torch.from_numpy(x) if isinstance(x, np.ndarray) else x
+        if xt.device.type != "cpu" or xt.dtype != torch.float32 or not xt.is_contiguous() \
+                or tuple(xt.shape) != tuple(self._feat_shape):
+            raise ValueError("run_host wants a contiguous float32 host array of shape %s" % (self._feat_shape,))
+        d = self._feat_shape[1]
+        if out is None:
+            out = torch.empty((self._num_rows, d), dtype=torch.float32).pin_memory()
+        if out.device.type != "cpu" or out.dtype != torch.float32 or not out.is_contiguous() \
+                or tuple(out.shape) != (self._num_rows, d):
+            raise ValueError("out must be a contiguous float32 host tensor of shape %s" % ((self._num_rows, d),))
         with torch.cuda.device(self._device):
-            xd = xt.to(self._device, non_blocking=True)
-            res = self.run([xd])
-            if out is None:
-                return res.cpu()
-            out.copy_(res, non_blocking=True)
-            torch.cuda.current_stream(self._device).synchronize()
-            return out
+            if self._num_col_partitions > 1:
+                # DDS layout: plain copy in, run, copy out
+                out.copy_(self.run([xt.to(self._device, non_blocking=True)]))
+                return out
+            if self._x_staging is None or tuple(self._x_staging.shape) != tuple(self._feat_shape):
+                self._x_staging = torch.empty(self._feat_shape, dtype=torch.float32, device=self._device)
+            dev.check(dev.lib().fg_spmm_csr_f32_host(
+                self._schedule, dev.ptr(self._adj_pos), dev.ptr(self._adj_idx), dev.ptr(self._adj_vals),
+                ctypes.c_void_p(xt.data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(self._x_staging),
+                dev.ptr(self.out), self._num_rows, self._num_cols, self._nnz, d, int(chunk),
+                dev.stream_ptr(self._device)))
+        return out
 
     def measure_average_time(self, inputs, num_runs):
         """Mean seconds per call over ``num_runs`` back-to-back calls (reference :163-186)."""

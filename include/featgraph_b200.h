@@ -87,13 +87,17 @@ void fg_row_schedule_destroy(fg_row_schedule* schedule);
  *              (power of two, 4..128), 0 = choose from n_cols and the L2 size.  It is the
  *              reference's num_feat_partitions idea (op/vanilla_spmm.py:41-44) used to keep
  *              the gathered slice of x resident in L2.  No effect on the values.
- * x: [n_cols, d], out: [n_rows, d].  Any d >= 1; 128-bit gathers need d % 4 == 0 and
+ *   ldx, ldo   row strides of x and out in floats (0 = d).  A stride larger than d computes a
+ *              window of d columns of wider matrices: pass x + c0 and out + c0 to work on columns
+ *              [c0, c0 + d).  Column windows are how the host-buffer calls below pipeline copies
+ *              against compute, and how sharded callers overlap the feature all-gather.
+ * x: [n_cols, d], out: [n_rows, d].  Any d >= 1; 128-bit gathers need d, ldx, ldo % 4 == 0 and
  * 16-byte aligned x / out, otherwise a scalar kernel runs.
  * -------------------------------------------------------------------------------------- */
 int fg_spmm_csr_f32(const fg_row_schedule* schedule, const int32_t* d_indptr,
-                    const int32_t* d_indices, const float* d_vals, const float* d_x, float* d_out,
-                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d, int32_t feat_tile,
-                    void* stream);
+                    const int32_t* d_indices, const float* d_vals, const float* d_x, int64_t ldx,
+                    float* d_out, int64_t ldo, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                    int32_t feat_tile, void* stream);
 
 /* SpMM, DDS (column-partitioned CSR made by util_convert_csr_to_dds,
  * python/featgraph/util/adj_partitioning.py:7-57):
@@ -104,8 +108,8 @@ int fg_spmm_csr_f32(const fg_row_schedule* schedule, const int32_t* d_indptr,
  * association of vanilla_spmm_dds_x86 (op/vanilla_spmm.py:195-218), called at
  * module/spmm.py:156-157. */
 int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
-                    const int32_t* d_s1_idx, const float* d_vals, const float* d_x, float* d_out,
-                    int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                    const int32_t* d_s1_idx, const float* d_vals, const float* d_x, int64_t ldx,
+                    float* d_out, int64_t ldo, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
                     int32_t num_col_partitions, int32_t feat_tile, void* stream);
 
 /* --------------------------------------------------------------------------------------
@@ -136,6 +140,10 @@ int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, co
  *   rows_sorted  non-zero promises that d_row is non-decreasing (a CSR-ordered edge list):
  *                the row-side feature row is then kept in registers across a row's edges.
  *                Zero is always safe.
+ *   ld_src, ld_dst  row strides in floats (0 = d); larger strides select a window of d columns
+ *                of wider matrices (pass src + c0, dst + c0).
+ *   accumulate   non-zero adds the dot products to what out already holds (a caller walking
+ *                column windows passes 0 for the first window and 1 afterwards).
  *   feat_tile    width in floats of the feature slice handled per pass over the edges (power
  *                of two, 4..512), 0 = the whole row if the column-side matrix fits in L2, else
  *                the widest slice that does.  With more than one pass, pass t > 0 adds its
@@ -145,9 +153,31 @@ int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, co
  * fixed tree (per-lane partial sums, then a butterfly; tiles in ascending order), not in
  * ascending k; the difference from the sequential sum is bounded by fp32 rounding of d terms.
  * -------------------------------------------------------------------------------------- */
-int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src,
-                     const float* d_dst, float* d_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
-                     int32_t d, int32_t rows_sorted, int32_t feat_tile, void* stream);
+int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src, int64_t ld_src,
+                     const float* d_dst, int64_t ld_dst, float* d_out, int64_t n_rows, int64_t n_cols,
+                     int64_t nnz, int32_t d, int32_t rows_sorted, int32_t accumulate, int32_t feat_tile,
+                     void* stream);
+
+/* --------------------------------------------------------------------------------------
+ * Host-buffer calls: features in HOST memory (h_*), results back to HOST memory, adjacency
+ * already on the device.  They replace the three steps a caller of the reference performs
+ * around the built function - tvm.nd.array(x_np, ctx), func(...), out.asnumpy()
+ * (tests/test_module_spmm.py:50-52, tests/test_module_sddmm.py:57-62) - and overlap them: the
+ * feature dimension is cut into column windows of `chunk` floats (0 = 64 for d >= 128, else one
+ * window), window c+1 is copied in while window c is computed and window c-1 is copied out.
+ * The caller supplies device staging buffers of the full shapes (d_*_staging); no device memory
+ * is allocated.  Pinned host memory gives full copy speed, pageable memory works.  The call
+ * returns when the host result is complete (it synchronises `stream`).  Values: SpMM as
+ * fg_spmm_csr_f32; SDDMM as fg_sddmm_coo_f32 with feat_tile = chunk.
+ * -------------------------------------------------------------------------------------- */
+int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indptr,
+                         const int32_t* d_indices, const float* d_vals, const float* h_x, float* h_out,
+                         float* d_x_staging, float* d_out_staging, int64_t n_rows, int64_t n_cols,
+                         int64_t nnz, int32_t d, int32_t chunk, void* stream);
+int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const float* h_src,
+                          const float* h_dst, float* h_out, float* d_src_staging, float* d_dst_staging,
+                          float* d_out_staging, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                          int32_t rows_sorted, int32_t chunk, void* stream);
 
 /* --------------------------------------------------------------------------------------
  * Index checks (the code generator of the reference emits shape asserts only; these add

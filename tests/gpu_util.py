@@ -54,7 +54,7 @@ def spmm_csr(indptr, indices, vals, x, feat_tile=0, use_schedule=True, check_gua
     ip, ix, vv, xx = dev(indptr, np.int32), dev(indices, np.int32), dev(vals, np.float32), dev(x, np.float32)
     buf, out = guarded(n_rows * d)
     sch = Schedule(ip, n_rows, long_row_threshold) if use_schedule else None
-    _native.check(L.fg_spmm_csr_f32(sch.h if sch else None, p(ip), p(ix), p(vv), p(xx), p(out), n_rows, n_cols,
+    _native.check(L.fg_spmm_csr_f32(sch.h if sch else None, p(ip), p(ix), p(vv), p(xx), 0, p(out), 0, n_rows, n_cols,
                                     len(indices), d, feat_tile, stream()))
     torch.cuda.synchronize()
     if check_guards:
@@ -73,7 +73,7 @@ def spmm_dds(s1_pos, s1_idx, vals, x, n_rows, parts, indptr_for_schedule=None, f
     sch = None
     if indptr_for_schedule is not None:
         sch = Schedule(dev(indptr_for_schedule, np.int32), n_rows)
-    _native.check(L.fg_spmm_dds_f32(sch.h if sch else None, p(pp), p(ii), p(vv), p(xx), p(out), n_rows, n_cols,
+    _native.check(L.fg_spmm_dds_f32(sch.h if sch else None, p(pp), p(ii), p(vv), p(xx), 0, p(out), 0, n_rows, n_cols,
                                     len(s1_idx), d, parts, feat_tile, stream()))
     torch.cuda.synchronize()
     assert guards_intact(buf), "kernel wrote outside its output"
@@ -86,8 +86,8 @@ def sddmm(row, col, src, dst, rows_sorted=0, feat_tile=0):
     n_rows = dst.shape[0]
     rr, cc, ss, dd = dev(row, np.int32), dev(col, np.int32), dev(src, np.float32), dev(dst, np.float32)
     buf, out = guarded(len(row))
-    _native.check(L.fg_sddmm_coo_f32(p(rr), p(cc), p(ss), p(dd), p(out), n_rows, n_cols, len(row), d,
-                                     int(rows_sorted), int(feat_tile), stream()))
+    _native.check(L.fg_sddmm_coo_f32(p(rr), p(cc), p(ss), 0, p(dd), 0, p(out), n_rows, n_cols, len(row), d,
+                                     int(rows_sorted), 0, int(feat_tile), stream()))
     torch.cuda.synchronize()
     assert guards_intact(buf), "kernel wrote outside its output"
     return out.cpu().numpy()

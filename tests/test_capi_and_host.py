@@ -40,13 +40,15 @@ def test_argument_errors_are_reported_not_raised_as_faults():
     """Host-side validation happens before any CUDA call, so it can be exercised here."""
     from featgraph_b200 import _native
     L = _native.lib()
-    rc = L.fg_spmm_csr_f32(None, None, None, None, None, None, 4, 4, 0, 0, 0, None)
+    rc = L.fg_spmm_csr_f32(None, None, None, None, None, 0, None, 0, 4, 4, 0, 0, 0, None)
     assert rc == 1 and b"bad sizes" in L.fg_last_error()
-    rc = L.fg_spmm_csr_f32(None, None, None, None, None, None, 4, 4, 0, 8, 48, None)
+    rc = L.fg_spmm_csr_f32(None, None, None, None, None, 0, None, 0, 4, 4, 0, 8, 48, None)
     assert rc == 1 and b"feat_tile" in L.fg_last_error()
-    rc = L.fg_sddmm_coo_f32(None, None, None, None, None, 4, 4, 5, 8, 0, 0, None)
+    rc = L.fg_sddmm_coo_f32(None, None, None, 0, None, 0, None, 4, 4, 5, 8, 0, 0, 0, None)
     assert rc == 1 and b"NULL" in L.fg_last_error()
-    assert L.fg_sddmm_coo_f32(None, None, None, None, None, 4, 4, 0, 8, 0, 0, None) == 0
+    assert L.fg_sddmm_coo_f32(None, None, None, 0, None, 0, None, 4, 4, 0, 8, 0, 0, 0, None) == 0
+    rc = L.fg_spmm_csr_f32(None, None, None, None, None, 4, None, 0, 4, 4, 0, 8, 0, None)
+    assert rc == 1 and b"row strides" in L.fg_last_error()
     with pytest.raises(_native.FeatGraphError):
         _native.check(rc)
 

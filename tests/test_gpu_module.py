@@ -69,6 +69,33 @@ def test_spmm_accepts_coo_input_and_run_host(adj_csr):
     np.testing.assert_allclose(adj_csr.dot(x), out.numpy(), rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("d,chunk", [(64, 0), (256, 0), (256, 32), (200, 64), (136, 0)])
+def test_host_buffer_calls_pipeline_windows_and_match_device_calls(oracle, d, chunk):
+    """run_host (copies pipelined over column windows) against run on device tensors, with pinned and
+    with pageable host memory."""
+    from featgraph_b200 import graphgen
+    adj = graphgen.power_law_graph(4000, 300_000, seed=51, kmax=3000)
+    n = adj.shape[0]
+    x = graphgen.uniform_features((n, d), seed=52)
+    y = graphgen.uniform_features((n, d), seed=53)
+    sp_ = VanillaSpMMcuda(adj)
+    sp_.build([placeholder((n, d))], {}, {})
+    want = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)
+    got_pageable = sp_.run_host([x], chunk=chunk).numpy().copy()
+    np.testing.assert_array_equal(got_pageable, want)
+    pinned_out = torch.empty((n, d)).pin_memory()
+    got = sp_.run_host([torch.from_numpy(x).pin_memory()], out=pinned_out, chunk=chunk)
+    assert got is pinned_out
+    np.testing.assert_array_equal(got.numpy(), want)
+    coo = adj.tocoo()
+    sd = VanillaSDDMMcuda(coo)
+    sd.build([placeholder((n, d)), placeholder((n, d))], {}, {})
+    e = sd.run_host([x, y], chunk=chunk).numpy()
+    np.testing.assert_allclose(e, oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)
+    with pytest.raises(ValueError):
+        sp_.run_host([x[:, :8].copy()])
+
+
 def test_spmm_build_and_run_argument_errors(adj_csr):
     module = VanillaSpMMcuda(adj_csr)
     with pytest.raises(TypeError):

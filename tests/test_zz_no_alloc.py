@@ -29,7 +29,7 @@ def _run_both(adj, x, feat_tile=0):
     # regular path: row schedule object + fg_spmm_csr_f32
     sch = G.Schedule(ip, n_rows)
     buf_a, out_a = G.guarded(n_rows * d)
-    _native.check(L.fg_spmm_csr_f32(sch.h, G.p(ip), G.p(ix), G.p(vv), G.p(xx), G.p(out_a), n_rows, n_cols,
+    _native.check(L.fg_spmm_csr_f32(sch.h, G.p(ip), G.p(ix), G.p(vv), G.p(xx), 0, G.p(out_a), 0, n_rows, n_cols,
                                     adj.nnz, d, feat_tile, G.stream()))
     # allocation-free path: inputs and outputs only
     buf_b, out_b = G.guarded(n_rows * d)
