@@ -92,8 +92,9 @@ struct Slice<1> {
     __device__ __forceinline__ void store(float* p) const { *p = v; }
 };
 
-// G lanes per (row, tile) unit; VEC floats per lane; DDS selects the two-level sum.
-template <int G, int VEC, bool DDS>
+// G lanes per (row, tile) unit; VEC floats per lane; DDS selects the two-level sum; UNIT: every
+// adjacency value is 1.0 (no value array is read, and 1.0 * x == x exactly, so nothing is multiplied).
+template <int G, int VEC, bool DDS, bool UNIT>
 __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a) {
     constexpr int CH = G < 8 ? G : 8;  // gathers issued back to back
     const int lane = threadIdx.x & 31;
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
         float my_v = 0.f;
         if (lig < len) {
             my_c = a.idx[start + lig];
-            my_v = a.vals[start + lig];
+            if (!UNIT) my_v = a.vals[start + lig];
         }
         for (int base = 0; base < max_len; base += G) {
             // next batch of indices / values, one iteration ahead of its use
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
             float nx_v = 0.f;
             if (base + G + lig < len) {
                 nx_c = a.idx[start + base + G + lig];
-                nx_v = a.vals[start + base + G + lig];
+                if (!UNIT) nx_v = a.vals[start + base + G + lig];
             }
 #pragma unroll
             for (int j0 = 0; j0 < G; j0 += CH) {
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
 #pragma unroll
                 for (int j = 0; j < CH; ++j) {
                     c[j] = __shfl_sync(0xffffffffu, my_c, j0 + j, G);
-                    v[j] = __shfl_sync(0xffffffffu, my_v, j0 + j, G);
+                    v[j] = UNIT ? 1.f : __shfl_sync(0xffffffffu, my_v, j0 + j, G);
                 }
                 // Unconditional loads (padding slots re-read row 0 of the slice) so that all
                 // CH gathers are in flight before the first dependent add.
@@ -163,7 +164,10 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
 #pragma unroll
                 for (int j = 0; j < CH; ++j) {
                     Slice<VEC> next = acc;
-                    next.axpy(v[j], xr[j]);
+                    if (UNIT)
+                        next.add(xr[j]);
+                    else
+                        next.axpy(v[j], xr[j]);
                     acc.select(c[j] >= 0, next);
                 }
             }
@@ -210,6 +214,7 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+template <bool UNIT>
 __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const SpmmArgs a) {
     extern __shared__ __align__(16) float ring_smem[];
     const int lane = threadIdx.x & 31;
@@ -239,13 +244,13 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
         v = 0.f;
         if (k < len) {
             c = a.idx[start + k];
-            v = a.vals[start + k];
+            if (!UNIT) v = a.vals[start + k];
         }
     };
     auto fill = [&](int stage, int c_mine, float v_mine) {
         float* slot = ring + (stage % kRingStages) * kSlotFloats;
         if (stage < n_stages) {
-            slot[kRingNnz * 32 + lane] = v_mine;
+            if (!UNIT) slot[kRingNnz * 32 + lane] = v_mine;
 #pragma unroll
             for (int i = 0; i < kRingNnz / 4; ++i) {
                 const int nz = i * 4 + sub;
@@ -286,7 +291,14 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
             __syncwarp();                // ... and so have the other lanes'
             const float* slot = ring + (s % kRingStages) * kSlotFloats;
             const int cnt = min(kRingNnz, len - s * kRingNnz);
-            if (cnt == kRingNnz) {
+            if (UNIT) {
+                if (cnt == kRingNnz) {
+#pragma unroll
+                    for (int j = 0; j < kRingNnz; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
+                } else {
+                    for (int j = 0; j < cnt; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
+                }
+            } else if (cnt == kRingNnz) {
 #pragma unroll
                 for (int j4 = 0; j4 < kRingNnz; j4 += 4) {
                     const float4 v = *reinterpret_cast<const float4*>(slot + kRingNnz * 32 + j4);
@@ -357,9 +369,15 @@ int launch_long(const SpmmArgs& a, cudaStream_t s) {
     if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
     if (blocks == 0) return FG_OK;
     static_assert(kLongSmemBytes <= 227 * 1024, "ring does not fit in shared memory");
-    FG_CUDA_TRY(cudaFuncSetAttribute(spmm_long_rows_kernel,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kLongSmemBytes));
-    spmm_long_rows_kernel<<<(unsigned)blocks, kLongThreads, kLongSmemBytes, s>>>(a);
+    if (a.vals == nullptr) {
+        FG_CUDA_TRY(cudaFuncSetAttribute(spmm_long_rows_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kLongSmemBytes));
+        spmm_long_rows_kernel<true><<<(unsigned)blocks, kLongThreads, kLongSmemBytes, s>>>(a);
+    } else {
+        FG_CUDA_TRY(cudaFuncSetAttribute(spmm_long_rows_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kLongSmemBytes));
+        spmm_long_rows_kernel<false><<<(unsigned)blocks, kLongThreads, kLongSmemBytes, s>>>(a);
+    }
     FG_CUDA_TRY(cudaGetLastError());
     fg::count_launches(1);
     return FG_OK;
@@ -372,10 +390,15 @@ int launch(const SpmmArgs& a, bool dds, cudaStream_t s) {
     const int64_t blocks = (n_units + units_per_block - 1) / units_per_block;
     if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
     if (blocks == 0) return FG_OK;
-    if (dds)
-        spmm_rows_kernel<G, VEC, true><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+    const bool unit = a.vals == nullptr;
+    if (dds && unit)
+        spmm_rows_kernel<G, VEC, true, true><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+    else if (dds)
+        spmm_rows_kernel<G, VEC, true, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+    else if (unit)
+        spmm_rows_kernel<G, VEC, false, true><<<(unsigned)blocks, kThreads, 0, s>>>(a);
     else
-        spmm_rows_kernel<G, VEC, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+        spmm_rows_kernel<G, VEC, false, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
     FG_CUDA_TRY(cudaGetLastError());
     fg::count_launches(1);
     return FG_OK;
@@ -424,7 +447,7 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
                         feat_tile);
     if (n_rows == 0) return FG_OK;
     if (!pos || !out) return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL position or output array");
-    if (nnz > 0 && (!idx || !vals || !x))
+    if (nnz > 0 && (!idx || !x))  // vals may be NULL: every value is 1.0
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL adjacency or feature array");
     if (schedule && fg_row_schedule_num_rows(schedule) != n_rows)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "row schedule was built for %lld rows, not %lld",

@@ -39,6 +39,9 @@ class SpMMbase:
         if adj_csr.data.dtype != np.float32:
             raise TypeError("float32 adjacency values are required, got %s" % adj_csr.data.dtype)
 
+        # an unweighted adjacency (all values exactly 1.0) needs no value array on the device
+        unit_values = bool(self._nnz == 0 or np.all(adj_csr.data == np.float32(1.0)))
+        self._unit_values = unit_values
         L = dev.lib()
         with torch.cuda.device(self._device):
             indptr = dev.upload(adj_csr.indptr, self._device)
@@ -56,11 +59,11 @@ class SpMMbase:
                 s1_pos, s1_idx, vals = util_convert_csr_to_dds(adj_csr, self._num_col_partitions)
                 self._adj_pos = dev.upload(s1_pos, self._device)
                 self._adj_idx = dev.upload(s1_idx, self._device)
-                self._adj_vals = dev.upload(vals, self._device)
+                self._adj_vals = None if unit_values else dev.upload(vals, self._device)
             else:
                 self._adj_pos = indptr
                 self._adj_idx = indices
-                self._adj_vals = dev.upload(adj_csr.data, self._device)
+                self._adj_vals = None if unit_values else dev.upload(adj_csr.data, self._device)
         self._feat_shape = None
         self._feat_tile = 0
         self._x_staging = None

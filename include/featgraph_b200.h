@@ -82,6 +82,10 @@ void fg_row_schedule_destroy(fg_row_schedule* schedule);
  * SpMM, CSR:  out[r, f] = sum_{e in [indptr[r], indptr[r+1])} vals[e] * x[indices[e], f]
  * Replaces the function built from vanilla_spmm_csr_x86 / vanilla_spmm_csr_cuda
  * (python/featgraph/op/vanilla_spmm.py:6-62, 83-125) and called at module/spmm.py:159-160.
+ *   d_vals     NULL means every adjacency value is 1.0 (an unweighted graph, as the reference's
+ *              dataset script stores it, benchmark/download_reddit_dataset.py:11): the value array is
+ *              then neither read nor multiplied in (1.0 * x == x exactly, so the result bits are
+ *              those of an all-ones value array).  Also accepted by the DDS and static entry points.
  *   schedule   NULL = visit rows in index order.
  *   feat_tile  width in floats of the feature slice handled per pass over the rows
  *              (power of two, 4..128), 0 = choose from n_cols and the L2 size.  It is the

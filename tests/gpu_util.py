@@ -51,7 +51,8 @@ def spmm_csr(indptr, indices, vals, x, feat_tile=0, use_schedule=True, check_gua
     L = _native.lib()
     n_rows = len(indptr) - 1
     n_cols, d = x.shape
-    ip, ix, vv, xx = dev(indptr, np.int32), dev(indices, np.int32), dev(vals, np.float32), dev(x, np.float32)
+    ip, ix, xx = dev(indptr, np.int32), dev(indices, np.int32), dev(x, np.float32)
+    vv = dev(vals, np.float32) if vals is not None else None  # None: unit values, no array
     buf, out = guarded(n_rows * d)
     sch = Schedule(ip, n_rows, long_row_threshold) if use_schedule else None
     _native.check(L.fg_spmm_csr_f32(sch.h if sch else None, p(ip), p(ix), p(vv), p(xx), 0, p(out), 0, n_rows, n_cols,

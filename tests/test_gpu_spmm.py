@@ -56,6 +56,25 @@ def test_unfused_rounding_is_the_one_matched(oracle):
     assert not np.array_equal(out, oracle.spmm_csr(a.indptr, a.indices, a.data, x, use_fma=True))
 
 
+@pytest.mark.parametrize("d", [3, 32, 64, 128])
+def test_unit_values_need_no_value_array(oracle, d):
+    """vals = NULL means all ones: same bits as an explicit all-ones array, long rows included, and
+    non-finite / signed-zero features pass through untouched."""
+    import gpu_util as G
+    from featgraph_b200 import graphgen
+    deg = np.array([0, 1, 7, 33, 1500, 64, 5000, 2, 31, 32], dtype=np.int64)
+    a = graphgen._csr_from_degrees(deg, 7000, seed=11)
+    x = graphgen.uniform_features((7000, d), seed=12 + d)
+    x[a.indices[0], 0] = -0.0
+    x[a.indices[5], d - 1] = np.inf
+    x[a.indices[2000], 1 % d] = np.nan
+    want = oracle.spmm_csr(a.indptr, a.indices, np.ones(a.nnz, np.float32), x)
+    for threshold in (0, 1024, 2 ** 31 - 1):
+        got = G.spmm_csr(a.indptr, a.indices, None, x, long_row_threshold=threshold)
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))  # bit patterns, NaN included
+    np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, None, x, use_schedule=False), want)
+
+
 def test_empty_rows_empty_matrix_and_single_row(oracle):
     import gpu_util as G
     # rows 0, 3 and the last are empty
