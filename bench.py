@@ -298,21 +298,13 @@ def run_ours(args):
                 continue
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
             ev[0].record(stream)
-            if spmm.windows is None:
-                spmm.gather(xd)
-                ev[1].record(stream)
-                spmm.compute()
-            else:
-                ev[1].record(stream)  # exchange overlapped with compute: timed as one
-                spmm.run(xd)
+            spmm.gather(xd)
+            ev[1].record(stream)
+            spmm.compute()
             ev[2].record(stream)
-            if sddmm.windows is None:
-                sddmm.gather(xd)
-                ev[3].record(stream)
-                sddmm.compute(yd)
-            else:
-                ev[3].record(stream)
-                sddmm.run(xd, yd)
+            sddmm.gather(xd)
+            ev[3].record(stream)
+            sddmm.compute(yd)
             ev[4].record(stream)
             record.append((d, ev))
 
@@ -481,18 +473,14 @@ def _install_build_cache(spmm, sddmm):
     def build_spmm(d, tile=0):
         if d not in cache_a:
             spmm.build(d, tile)
-            cache_a[d] = (spmm.module.out, spmm.x_full, spmm.module._feat_shape, spmm.module._feat_tile,
-                          spmm.windows, getattr(spmm, "win_send", None), getattr(spmm, "win_full", None))
-        (spmm.module.out, spmm.x_full, spmm.module._feat_shape, spmm.module._feat_tile, spmm.windows,
-         spmm.win_send, spmm.win_full) = cache_a[d]
+            cache_a[d] = (spmm.module.out, spmm.x_full, spmm.module._feat_shape, spmm.module._feat_tile)
+        spmm.module.out, spmm.x_full, spmm.module._feat_shape, spmm.module._feat_tile = cache_a[d]
 
     def build_sddmm(d):
         if d not in cache_b:
             sddmm.build(d)
-            cache_b[d] = (sddmm.module.out, sddmm.src_full, sddmm.module._shapes, sddmm.windows,
-                          getattr(sddmm, "win_send", None), getattr(sddmm, "win_full", None))
-        (sddmm.module.out, sddmm.src_full, sddmm.module._shapes, sddmm.windows, sddmm.win_send,
-         sddmm.win_full) = cache_b[d]
+            cache_b[d] = (sddmm.module.out, sddmm.src_full, sddmm.module._shapes)
+        sddmm.module.out, sddmm.src_full, sddmm.module._shapes = cache_b[d]
 
     spmm.build_cached = build_spmm
     sddmm.build_cached = build_sddmm

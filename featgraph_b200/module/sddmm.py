@@ -123,26 +123,6 @@ class SDDMMbase:
                                              self._rows_sorted, 0, self._feat_tile,
                                              dev.stream_ptr(self._device)))
 
-    def run_window(self, src_window, dst, col0, width, accumulate):
-        """Add (or, with ``accumulate=False``, store) the part of every dot product that comes from
-        feature columns ``[col0, col0 + width)``: ``src_window`` is a ``[num_cols, width]`` device
-        tensor with those columns of the column-side matrix, ``dst`` the whole row-side matrix."""
-        if self.out is None:
-            raise RuntimeError("call build() before run_window()")
-        import ctypes
-        d = self._shapes[0][1]
-        assert 0 <= col0 and col0 + width <= d and src_window.shape == (self._num_cols, width)
-        assert src_window.stride(1) == 1 and src_window.dtype == torch.float32
-        dev.check_input(dst, self._shapes[1], self._device, "row-side features")
-        dst_view = dst[:, col0:col0 + width]
-        with torch.cuda.device(self._device):
-            dev.check(dev.lib().fg_sddmm_coo_f32(
-                dev.ptr(self._adj_row), dev.ptr(self._adj_col), ctypes.c_void_p(src_window.data_ptr()),
-                src_window.stride(0), ctypes.c_void_p(dst_view.data_ptr()), d, dev.ptr(self.out),
-                self._num_rows, self._num_cols, self._nnz, width, self._rows_sorted, 1 if accumulate else 0, 0,
-                dev.stream_ptr(self._device)))
-        return self.out
-
     def run(self, inputs):
         """Enqueue the kernel on the current stream; returns the module's output tensor (the
         same object every call, reference :115-129).  Argument order: [column-side, row-side]."""

@@ -148,24 +148,6 @@ class SpMMbase:
                                    self._feat_tile, s)
         dev.check(rc)
 
-    def run_window(self, x_window, col0, width):
-        """Compute output columns ``[col0, col0 + width)`` from ``x_window``, a ``[num_cols, width]``
-        (possibly strided) device tensor holding the same columns of the feature matrix.  Used by
-        callers that produce the features window by window (sharded all-gather); plain CSR only."""
-        if self.out is None:
-            raise RuntimeError("call build() before run_window()")
-        assert self._num_col_partitions == 1, "column windows are for the CSR layout"
-        d = self._feat_shape[1]
-        assert 0 <= col0 and col0 + width <= d and x_window.shape == (self._num_cols, width)
-        assert x_window.stride(1) == 1 and x_window.dtype == torch.float32 and x_window.device == self._device
-        out_view = self.out[:, col0:col0 + width]
-        with torch.cuda.device(self._device):
-            dev.check(dev.lib().fg_spmm_csr_f32(
-                self._schedule, dev.ptr(self._adj_pos), dev.ptr(self._adj_idx), dev.ptr(self._adj_vals),
-                ctypes.c_void_p(x_window.data_ptr()), x_window.stride(0), ctypes.c_void_p(out_view.data_ptr()), d,
-                self._num_rows, self._num_cols, self._nnz, width, 0, dev.stream_ptr(self._device)))
-        return self.out
-
     def run(self, inputs):
         """Enqueue the kernel on the current stream and return the module's output tensor
         (the same object every call, as the reference returns ``out_tvm``, :142-161)."""

@@ -24,10 +24,6 @@ import torch.distributed as dist
 from .util import nnz_balanced_row_ranges
 
 
-# Width (floats) of the column windows the overlapped exchange works in: one L2-sized feature slice.
-WINDOW = 64
-
-
 def shard_csr_rows(adj_csr, bounds, rank):
     """Rows ``[bounds[rank], bounds[rank+1])`` of a CSR matrix as a CSR matrix of the same width:
     indptr rebased to start at 0, column ids untouched."""
@@ -121,30 +117,6 @@ class _ShardedBase:
     def _gather(self, padded, local):
         return all_gather_padded(padded, local, self.bounds, self.group)
 
-    # -- windowed exchange: the all-gather of column window c+1 runs while window c is computed --
-    def _windows(self, feat_len):
-        """Column windows for the overlapped path, or None when one gather is all there is to do."""
-        if self.world == 1 or feat_len < 2 * WINDOW or not dist.is_initialized() \
-                or dist.get_backend(self.group) != "nccl":
-            return None
-        return [(c0, min(WINDOW, feat_len - c0)) for c0 in range(0, feat_len, WINDOW)]
-
-    def _alloc_windows(self, windows):
-        """Per window: this rank's slot-sized send buffer and the gathered [world*slot, width] buffer."""
-        send = [torch.zeros((self.slot, w), dtype=torch.float32, device=self.device) for _, w in windows]
-        full = [torch.zeros((self.world * self.slot, w), dtype=torch.float32, device=self.device) for _, w in windows]
-        return send, full
-
-    def _start_window_gathers(self, windows, send, full, local):
-        """Re-lay this rank's rows window-major and start one all-gather per window; returns the work
-        handles in window order (NCCL runs them one after another on its own stream)."""
-        rows = self.row_hi - self.row_lo
-        works = []
-        for (c0, w), sbuf, fbuf in zip(windows, send, full):
-            sbuf[:rows].copy_(local[:, c0:c0 + w])
-            works.append(dist.all_gather_into_tensor(fbuf, sbuf, group=self.group, async_op=True))
-        return works
-
 
 class ShardedSpMM(_ShardedBase):
     """Row-sharded SpMM for a square adjacency.
@@ -166,12 +138,7 @@ class ShardedSpMM(_ShardedBase):
     def build(self, feat_len, feat_tile=0):
         from .placeholder import placeholder
         self.module.build([placeholder((self.n, feat_len))], {}, {"feat_tile": feat_tile})
-        self.windows = self._windows(feat_len)
-        if self.windows is None:
-            self.x_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
-        else:
-            self.x_full = None
-            self.win_send, self.win_full = self._alloc_windows(self.windows)
+        self.x_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, x_local):
         """The exchange step alone: every rank's feature rows into this rank's ``x_full``."""
@@ -182,17 +149,9 @@ class ShardedSpMM(_ShardedBase):
         return self.module.run([self.x_full])
 
     def run(self, x_local):
-        """x_local: this rank's rows of the feature matrix.  Returns this rank's rows of A.X.
-        For feature lengths of two windows or more the all-gather is issued window by window and each
-        window's kernel starts as soon as its slice has arrived."""
-        if self.windows is None:
-            self.gather(x_local)
-            return self.compute()
-        works = self._start_window_gathers(self.windows, self.win_send, self.win_full, x_local)
-        for (c0, w), fbuf, work in zip(self.windows, self.win_full, works):
-            work.wait()  # the compute stream waits for this window's gather only
-            self.module.run_window(fbuf, c0, w)
-        return self.module.out
+        """x_local: this rank's rows of the feature matrix.  Returns this rank's rows of A.X."""
+        self.gather(x_local)
+        return self.compute()
 
 
 class ShardedSDDMM(_ShardedBase):
@@ -210,12 +169,7 @@ class ShardedSDDMM(_ShardedBase):
     def build(self, feat_len):
         from .placeholder import placeholder
         self.module.build([placeholder((self.n, feat_len)), placeholder((self.row_hi - self.row_lo, feat_len))], {}, {})
-        self.windows = self._windows(feat_len)
-        if self.windows is None:
-            self.src_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
-        else:
-            self.src_full = None
-            self.win_send, self.win_full = self._alloc_windows(self.windows)
+        self.src_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, src_local):
         return self._gather(self.src_full, src_local)
@@ -226,11 +180,5 @@ class ShardedSDDMM(_ShardedBase):
     def run(self, src_local, dst_local):
         """src_local: this rank's rows of the column-side matrix (gathered from all ranks);
         dst_local: this rank's rows of the row-side matrix.  Returns this rank's edges' dots."""
-        if self.windows is None:
-            self.gather(src_local)
-            return self.compute(dst_local)
-        works = self._start_window_gathers(self.windows, self.win_send, self.win_full, src_local)
-        for i, ((c0, w), fbuf, work) in enumerate(zip(self.windows, self.win_full, works)):
-            work.wait()
-            self.module.run_window(fbuf, dst_local, c0, w, accumulate=i > 0)
-        return self.module.out
+        self.gather(src_local)
+        return self.compute(dst_local)

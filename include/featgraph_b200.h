@@ -94,7 +94,7 @@ void fg_row_schedule_destroy(fg_row_schedule* schedule);
  *   ldx, ldo   row strides of x and out in floats (0 = d).  A stride larger than d computes a
  *              window of d columns of wider matrices: pass x + c0 and out + c0 to work on columns
  *              [c0, c0 + d).  Column windows are how the host-buffer calls below pipeline copies
- *              against compute, and how sharded callers overlap the feature all-gather.
+ *              against compute.
  * x: [n_cols, d], out: [n_rows, d].  Any d >= 1; 128-bit gathers need d, ldx, ldo % 4 == 0 and
  * 16-byte aligned x / out, otherwise a scalar kernel runs.
  * -------------------------------------------------------------------------------------- */
