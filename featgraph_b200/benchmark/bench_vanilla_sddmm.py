@@ -10,7 +10,7 @@ import numpy as np
 import scipy.sparse
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from featgraph import placeholder  # noqa: E402
 from featgraph.module import VanillaSDDMMcuda, VanillaSDDMMx86  # noqa: E402
 
