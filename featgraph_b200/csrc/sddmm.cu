@@ -25,6 +25,8 @@
 // Arithmetic: fp32 FMA inside a lane, fixed-shape tree across lanes, ascending order across
 // tiles.  Not the sequential k order of the x86 loop; the difference is bounded by fp32
 // rounding of d terms.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -57,7 +59,7 @@ struct SddmmArgs {
 // CACHE_DST: edge list is row-sorted, keep the row-side slice in registers.
 // MASKED: the tile is narrower than 4*G*NV floats (ragged last tile).
 template <int G, int NV, int U, bool CACHE_DST, bool MASKED>
-__global__ void __launch_bounds__(kThreads, (NV >= 3 || (NV == 2 && !CACHE_DST)) ? 3 : 4) sddmm_tile_kernel(const SddmmArgs a) {
+__global__ void __launch_bounds__(kThreads, NV >= 2 ? 2 : 4) sddmm_tile_kernel(const SddmmArgs a) {
     static_assert(G % U == 0, "U must divide G");
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
@@ -74,6 +76,10 @@ __global__ void __launch_bounds__(kThreads, (NV >= 3 || (NV == 2 && !CACHE_DST))
         if (!ok[i]) colv[i] = 0;
     }
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 dcache[NV];  // row-side slice of cur_row (meaningful with CACHE_DST only)
+#pragma unroll
+    for (int i = 0; i < NV; ++i) dcache[i] = zero4;
+    int cur_row = -1;
 
     // ids of the first batch; each batch then requests the next one's before it starts gathering,
     // so the id fetch (a DRAM stream) overlaps the previous batch instead of preceding the gathers
@@ -97,76 +103,89 @@ __global__ void __launch_bounds__(kThreads, (NV >= 3 || (NV == 2 && !CACHE_DST))
         }
         float prev = 0.f;  // earlier tiles' partial dot product
         if (a.accumulate && valid) prev = a.out[e];
-        // bit l set: edge l starts a new row relative to edge l-1 (always set at a group's
-        // first edge so that each group loads its first row)
-        unsigned change = 0;
-        if (CACHE_DST) {
-            const int r_prev = __shfl_up_sync(0xffffffffu, r_l, 1);
-            change = __ballot_sync(0xffffffffu, lig == 0 || r_prev != r_l);
-        }
-
+        // Row side.  ONE_ROW: all 32 edges of the batch share a row (the common case in a row-sorted
+        // list with long rows): its slice is loaded once, and only if it differs from the previous
+        // batch's.  Otherwise a ballot marks where rows change (bit l: edge l starts a new row; always
+        // set at a group's first edge) and each group reloads at its marks.
         float r[G / U];  // one partly reduced value per chunk of U edges
-        float4 dcache[NV];
-#pragma unroll
-        for (int i = 0; i < NV; ++i) dcache[i] = zero4;
-
-#pragma unroll
-        for (int s = 0; s < G; s += U) {
-            int c[U], rr[U];
-            float pc[U];
-            float4 xs[U][NV];
-            float4 xd[U][NV];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                c[u] = __shfl_sync(0xffffffffu, c_l, gbase + s + u);
-                if (!CACHE_DST) rr[u] = __shfl_sync(0xffffffffu, r_l, gbase + s + u);
+        auto run_batch = [&](auto one_row_tag) {
+            constexpr bool ONE_ROW = decltype(one_row_tag)::value;
+            unsigned change = 0;
+            if (CACHE_DST && !ONE_ROW) {
+                const int r_prev = __shfl_up_sync(0xffffffffu, r_l, 1);
+                change = __ballot_sync(0xffffffffu, lig == 0 || r_prev != r_l);
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const float* ps = a.src + (int64_t)c[u] * a.ld_src;
+            for (int s = 0; s < G; s += U) {
+                int c[U], rr[U];
+                float pc[U];
+                float4 xs[U][NV];
+                float4 xd[U][NV];
 #pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    xs[u][i] = fg::ldg4(ps + colv[i]);
-                    if (MASKED && !ok[i]) xs[u][i] = zero4;
+                for (int u = 0; u < U; ++u) {
+                    c[u] = __shfl_sync(0xffffffffu, c_l, gbase + s + u);
+                    if (!CACHE_DST) rr[u] = __shfl_sync(0xffffffffu, r_l, gbase + s + u);
                 }
-                if (!CACHE_DST) {
-                    const float* pd = a.dst + (int64_t)rr[u] * a.ld_dst;
 #pragma unroll
-                    for (int i = 0; i < NV; ++i) xd[u][i] = fg::ldg4(pd + colv[i]);
-                }
-            }
+                for (int u = 0; u < U; ++u) {
+                    const float* ps = a.src + (int64_t)c[u] * a.ld_src;
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                float acc = 0.f;
-                if (CACHE_DST) {
-                    if ((change >> (gbase + s + u)) & 1u) {  // uniform within the group
-                        const int rnew = __shfl_sync(gmask, r_l, gbase + s + u);
-                        const float* pd = a.dst + (int64_t)rnew * a.ld_dst;
-#pragma unroll
-                        for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
+                    for (int i = 0; i < NV; ++i) {
+                        xs[u][i] = fg::ldg4(ps + colv[i]);
+                        if (MASKED && !ok[i]) xs[u][i] = zero4;
                     }
+                    if (!CACHE_DST) {
+                        const float* pd = a.dst + (int64_t)rr[u] * a.ld_dst;
 #pragma unroll
-                    for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], dcache[i]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], xd[u][i]);
+                        for (int i = 0; i < NV; ++i) xd[u][i] = fg::ldg4(pd + colv[i]);
+                    }
                 }
-                pc[u] = acc;
-            }
-            // first log2(U) steps of the transposed butterfly, inside the chunk: afterwards pc[0] on a
-            // lane holds, for the chunk's edge picked by the lane's low bits, the sum over the 2^k
-            // lanes that differ from it in those bits
 #pragma unroll
-            for (int off = 1; off < U; off <<= 1) {
-                const bool upper = (lig & off) != 0;
+                for (int u = 0; u < U; ++u) {
+                    float acc = 0.f;
+                    if (CACHE_DST) {
+                        if (!ONE_ROW && ((change >> (gbase + s + u)) & 1u)) {  // uniform within the group
+                            const int rnew = __shfl_sync(gmask, r_l, gbase + s + u);
+                            const float* pd = a.dst + (int64_t)rnew * a.ld_dst;
 #pragma unroll
-                for (int i = 0; i < U / (2 * off); ++i) {
-                    const float send = upper ? pc[2 * i] : pc[2 * i + 1];
-                    const float keep = upper ? pc[2 * i + 1] : pc[2 * i];
-                    pc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                            for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], dcache[i]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], xd[u][i]);
+                    }
+                    pc[u] = acc;
                 }
+                // first log2(U) steps of the transposed butterfly, inside the chunk: afterwards pc[0]
+                // on a lane holds, for the chunk's edge picked by the lane's low bits, the sum over
+                // the 2^k lanes that differ from it in those bits
+#pragma unroll
+                for (int off = 1; off < U; off <<= 1) {
+                    const bool upper = (lig & off) != 0;
+#pragma unroll
+                    for (int i = 0; i < U / (2 * off); ++i) {
+                        const float send = upper ? pc[2 * i] : pc[2 * i + 1];
+                        const float keep = upper ? pc[2 * i + 1] : pc[2 * i];
+                        pc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                    }
+                }
+                r[s / U] = pc[0];
             }
-            r[s / U] = pc[0];
+        };
+        const int r_first = __shfl_sync(0xffffffffu, r_l, 0);
+        if (CACHE_DST && __all_sync(0xffffffffu, r_l == r_first)) {
+            if (r_first != cur_row) {
+                cur_row = r_first;
+                const float* pd = a.dst + (int64_t)r_first * a.ld_dst;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
+            }
+            run_batch(std::true_type{});
+        } else {
+            run_batch(std::false_type{});
+            cur_row = -1;  // the groups ended on different rows
         }
 
         // remaining steps across the chunks: afterwards r[0] on lane i of the group is edge i's total
