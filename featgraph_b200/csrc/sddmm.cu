@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kThreads, NV >= 2 ? 2 : 4) sddmm_tile_kernel(c
         if (!ok[i]) colv[i] = 0;
     }
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int ld_src = (int)a.ld_src, ld_dst = (int)a.ld_dst;  // 32 x 32 -> 64 bit multiply per gather
     float4 dcache[NV];  // row-side slice of cur_row (meaningful with CACHE_DST only)
 #pragma unroll
     for (int i = 0; i < NV; ++i) dcache[i] = zero4;
@@ -128,14 +129,14 @@ __global__ void __launch_bounds__(kThreads, NV >= 2 ? 2 : 4) sddmm_tile_kernel(c
                 }
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const float* ps = a.src + (int64_t)c[u] * a.ld_src;
+                    const float* ps = a.src + (int64_t)c[u] * ld_src;
 #pragma unroll
                     for (int i = 0; i < NV; ++i) {
                         xs[u][i] = fg::ldg4(ps + colv[i]);
                         if (MASKED && !ok[i]) xs[u][i] = zero4;
                     }
                     if (!CACHE_DST) {
-                        const float* pd = a.dst + (int64_t)rr[u] * a.ld_dst;
+                        const float* pd = a.dst + (int64_t)rr[u] * ld_dst;
 #pragma unroll
                         for (int i = 0; i < NV; ++i) xd[u][i] = fg::ldg4(pd + colv[i]);
                     }
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, NV >= 2 ? 2 : 4) sddmm_tile_kernel(c
                     if (CACHE_DST) {
                         if (!ONE_ROW && ((change >> (gbase + s + u)) & 1u)) {  // uniform within the group
                             const int rnew = __shfl_sync(gmask, r_l, gbase + s + u);
-                            const float* pd = a.dst + (int64_t)rnew * a.ld_dst;
+                            const float* pd = a.dst + (int64_t)rnew * ld_dst;
 #pragma unroll
                             for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
                         }
@@ -178,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, NV >= 2 ? 2 : 4) sddmm_tile_kernel(c
         if (CACHE_DST && __all_sync(0xffffffffu, r_l == r_first)) {
             if (r_first != cur_row) {
                 cur_row = r_first;
-                const float* pd = a.dst + (int64_t)r_first * a.ld_dst;
+                const float* pd = a.dst + (int64_t)r_first * ld_dst;
 #pragma unroll
                 for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
             }
@@ -305,8 +306,8 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
                         feat_tile);
     if (ld_src == 0) ld_src = d;
     if (ld_dst == 0) ld_dst = d;
-    if (ld_src < d || ld_dst < d)
-        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row strides ld_src=%lld ld_dst=%lld must be 0 or >= d=%d",
+    if (ld_src < d || ld_dst < d || ld_src > INT32_MAX || ld_dst > INT32_MAX)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row strides ld_src=%lld ld_dst=%lld must be 0 or in [d=%d, 2^31)",
                         (long long)ld_src, (long long)ld_dst, d);
     if (nnz == 0) return FG_OK;
     if (!d_row || !d_col || !d_src || !d_dst || !d_out)
@@ -330,11 +331,11 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
     // not even a 32-float slice does); otherwise the widest power of two whose slice fits.
     int tile = feat_tile;
     if (tile == 0) {
-        // A single pass wins whenever the whole matrix is about L2-sized (no second read of
+        // A single pass wins while the whole matrix fits three quarters of L2 (no second read of
         // the edge list, no read-modify-write of out); a slice should fit in half of L2.
         const int64_t l2 = l2_size_bytes();
         const int64_t budget = l2 / 2;
-        if (n_cols * (int64_t)d * 4 <= l2 - l2 / 20 || n_cols * 32 * 4 > budget) {
+        if (n_cols * (int64_t)d * 4 <= l2 - l2 / 4 || n_cols * 32 * 4 > budget) {
             tile = d <= 512 ? d : 512;
         } else {
             tile = 32;

@@ -123,7 +123,9 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
             start = p[0];
             len = p[1] - start;
         }
-        const int64_t col_base = DDS ? (int64_t)k * a.cols_per_part : 0;
+        // partition k's first column folded into the base pointer; a 32 x 32 -> 64 bit multiply per gather
+        const float* xbase = DDS ? xcol + (int64_t)k * a.cols_per_part * a.ldx : xcol;
+        const int ldx32 = (int)a.ldx;
         Slice<VEC> acc;
         acc.zero();
 
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
                 // CH gathers are in flight before the first dependent add.
 #pragma unroll
                 for (int j = 0; j < CH; ++j)
-                    xr[j].load(xcol + (col_base + (c[j] < 0 ? 0 : c[j])) * a.ldx);
+                    xr[j].load(xbase + (int64_t)(c[j] < 0 ? 0 : c[j]) * ldx32);
                 // Branch-free commit: a branch here would let the compiler sink each load
                 // next to its use and serialise the gathers.
 #pragma unroll
@@ -237,6 +239,7 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
     const int sub = lane >> 3;
     const bool piece_ok = col0 + piece * 4 < a.d;  // ragged last tile (d % 4 == 0)
     const float* xpiece = a.x + col0 + piece * 4;
+    const int ldx32 = (int)a.ldx;
 
     auto fetch_ids = [&](int stage, int& c, float& v) {  // nonzero `lane` of `stage`
         const int k = stage * kRingNnz + lane;
@@ -255,7 +258,7 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
             for (int i = 0; i < kRingNnz / 4; ++i) {
                 const int nz = i * 4 + sub;
                 const int c = __shfl_sync(0xffffffffu, c_mine, nz);
-                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * a.ldx);
+                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * ldx32);
             }
         }
         cp_async_commit();  // one group per stage, empty past the end, so the wait count is fixed
@@ -439,8 +442,8 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     if (parts < 1) return fg::fail(FG_ERR_INVALID_ARGUMENT, "num_col_partitions must be >= 1");
     if (ldx == 0) ldx = d;
     if (ldo == 0) ldo = d;
-    if (ldx < d || ldo < d)
-        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row strides ldx=%lld ldo=%lld must be 0 or >= d=%d",
+    if (ldx < d || ldo < d || ldx > INT32_MAX || ldo > INT32_MAX)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row strides ldx=%lld ldo=%lld must be 0 or in [d=%d, 2^31)",
                         (long long)ldx, (long long)ldo, d);
     if (feat_tile != 0 && (feat_tile < 4 || feat_tile > 128 || (feat_tile & (feat_tile - 1))))
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "feat_tile=%d: want 0 or a power of two in 4..128",
