@@ -62,7 +62,10 @@ def parse_args():
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--dims", default="32,64,128,256,512")
+    p.add_argument("--dims", default=None, help="feature lengths (default 32,64,128,256,512; 128 for C4)")
+    p.add_argument("--workload", default="C2", choices=["C2", "C4"],
+                   help="C2: power-law graph, SpMM and SDDMM at each d (the headline); C4: R-MAT scale 22, "
+                        "H = A.X then out[e] = dot(H[row e], Y[col e]) at d = 128")
     p.add_argument("--shrink", type=int, default=1, help="divide node count (debug / profiling runs)")
     p.add_argument("--feat-tile", type=int, default=0)
     p.add_argument("--no-e2e", action="store_true")
@@ -198,7 +201,11 @@ def run_reference_arm(args):
     from featgraph_b200 import graphgen
     n, nnz, kmax = graph_params(args.shrink)
     t0 = time.time()
-    adj = graphgen.power_law_graph(n, nnz, graphgen.WORKLOADS[WORKLOAD]["seed"], kmax=kmax)
+    if WORKLOAD == "C4":
+        adj = graphgen.rmat_graph(22 - int(np.log2(args.shrink)), 32, graphgen.WORKLOADS[WORKLOAD]["seed"])
+        n, nnz = adj.shape[0], adj.nnz
+    else:
+        adj = graphgen.power_law_graph(n, nnz, graphgen.WORKLOADS[WORKLOAD]["seed"], kmax=kmax)
     log("graph built in %.1fs" % (time.time() - t0))
     d = 64
     sample_edges = nnz // 16
@@ -210,13 +217,15 @@ def run_reference_arm(args):
     wall = time.perf_counter() - t0
     line = {
         "impl": "reference", "metric": "spmm_sddmm_gflops", "value": r["step_gflops"], "unit": "GFLOP/s",
-        "n_gpus": 0, "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * (r["seconds"]["spmm"] + r["seconds"]["sddmm_sample"]),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "C2/C3 power-law graph %d nodes / %d edges, SpMM+SDDMM, fp32" % (n, nnz),
-                   "dims": [d], "note": "CPU restatement of the reference's x86 path (the reference itself "
-                   "needs a code generator that is not installed); SpMM on all host threads, SDDMM on one "
-                   "thread as in the reference's schedule"},
+        "config": {"workload": "C2/C3 power-law graph %d nodes / %d edges: SpMM + SDDMM at each d" % (n, nnz),
+                   "dims": [int(x) for x in args.dims.split(",")], "sample_dims": [d],
+                   "note": "host cores only (no GPU is used, whatever --gpus says): the CPU restatement of the "
+                           "reference's x86 path (the reference itself needs a code generator that is not "
+                           "installed); each step is a bounded sample, SpMM at d=%d on all host threads and "
+                           "SDDMM at d=%d on one thread as in the reference's schedule" % (d, d)},
         "cpu_baseline": {"value": r["step_gflops"], "unit": "GFLOP/s", "cores": r["threads"], "kind": "port",
                          "sample": "SpMM d=%d whole graph; SDDMM d=%d first %d edges" % (d, d, r["sddmm_edges"]),
                          "detail": r},
@@ -255,14 +264,28 @@ def run_ours(args):
     n, nnz, kmax = graph_params(args.shrink)
     seed = graphgen.WORKLOADS[WORKLOAD]["seed"]
 
-    # --- inputs: every rank derives the degree sequence, then generates only its own rows ---
+    # --- inputs ---
     t0 = time.time()
-    deg = graphgen.power_law_degrees(n, nnz, seed, kmax=kmax)
-    indptr_all = np.zeros(n + 1, dtype=np.int64)
-    np.cumsum(deg, out=indptr_all[1:])
-    bounds = nnz_balanced_row_ranges(indptr_all, world)
-    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
-    local_adj = graphgen._csr_from_degrees(deg[lo:hi], n, seed + 1, row_offset=lo)
+    if WORKLOAD == "C4":
+        # R-MAT: every rank generates the whole graph (seeded, identical) and keeps its rows
+        os.environ["OMP_NUM_THREADS"] = str(max(1, len(os.sched_getaffinity(0)) // world))
+        from featgraph_b200.sharded import shard_csr_rows
+        whole_adj = graphgen.rmat_graph(22 - int(np.log2(args.shrink)), 32, seed)
+        n, nnz = whole_adj.shape[0], whole_adj.nnz
+        deg = np.diff(whole_adj.indptr).astype(np.int64)
+        bounds = nnz_balanced_row_ranges(whole_adj.indptr, world)
+        lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+        local_adj = shard_csr_rows(whole_adj, bounds, rank)
+        if world > 1:
+            del whole_adj
+    else:
+        # power law: every rank derives the degree sequence, then generates only its own rows
+        deg = graphgen.power_law_degrees(n, nnz, seed, kmax=kmax)
+        indptr_all = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(deg, out=indptr_all[1:])
+        bounds = nnz_balanced_row_ranges(indptr_all, world)
+        lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+        local_adj = graphgen._csr_from_degrees(deg[lo:hi], n, seed + 1, row_offset=lo)
     local_nnz = local_adj.nnz
     log("[rank %d] rows [%d,%d) nnz %d built in %.1fs" % (rank, lo, hi, local_nnz, time.time() - t0))
 
@@ -293,18 +316,21 @@ def run_ours(args):
             spmm.build_cached(d, args.feat_tile)
             sddmm.build_cached(d)
             if record is None:
-                spmm.run(xd)
-                sddmm.run(xd, yd)
+                h = spmm.run(xd)
+                if WORKLOAD == "C4":
+                    sddmm.run(yd, h)  # column side Y (gathered), row side H = A.X (local rows)
+                else:
+                    sddmm.run(xd, yd)
                 continue
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
             ev[0].record(stream)
             spmm.gather(xd)
             ev[1].record(stream)
-            spmm.compute()
+            h = spmm.compute()
             ev[2].record(stream)
-            sddmm.gather(xd)
+            sddmm.gather(yd if WORKLOAD == "C4" else xd)
             ev[3].record(stream)
-            sddmm.compute(yd)
+            sddmm.compute(h if WORKLOAD == "C4" else yd)
             ev[4].record(stream)
             record.append((d, ev))
 
@@ -360,8 +386,8 @@ def run_ours(args):
                 sddmm.build_cached(d)
                 if world == 1:
                     # the library's host-buffer calls: copies pipelined against the kernels
-                    spmm.module.run_host([xh], out=outs_host[d][0])
-                    sddmm.module.run_host([xh, yh], out=outs_host[d][1])
+                    hh = spmm.module.run_host([xh], out=outs_host[d][0])
+                    sddmm.module.run_host([yh, hh] if WORKLOAD == "C4" else [xh, yh], out=outs_host[d][1])
                     continue
                 xd = xh.to(device, non_blocking=True)
                 outs_host[d][0].copy_(spmm.run(xd), non_blocking=True)
@@ -431,7 +457,9 @@ def run_ours(args):
         "metric": "spmm_sddmm_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "C2/C3 power-law graph %d nodes / %d edges: SpMM + SDDMM at each d" % (n, nnz),
+        "config": {"workload": ("C4 R-MAT graph %d nodes / %d edges: H = A.X then out[e] = dot(H[row e], Y[col e])"
+                                if WORKLOAD == "C4" else
+                                "C2/C3 power-law graph %d nodes / %d edges: SpMM + SDDMM at each d") % (n, nnz),
                    "dims": dims, "parallelism": "row-sharded x%d (nnz-balanced), features all-gathered per call"
                    % world if world > 1 else "single GPU",
                    "l2_policy": "inputs larger than L2 (CSR arrays %.0f MB per pass; 10 different kernels "
@@ -442,8 +470,7 @@ def run_ours(args):
     }
     if not args.no_cpu_baseline and world == 1:
         t0 = time.time()
-        whole = graphgen._csr_from_degrees(deg, n, seed + 1) if world > 1 else local_adj
-        r = cpu_reference_rates(whole, 64, nnz // 16, 1)
+        r = cpu_reference_rates(local_adj, 64, nnz // 16, 1)
         line["cpu_baseline"] = {
             "value": r["step_gflops"], "unit": "GFLOP/s", "cores": r["threads"], "kind": "port",
             "sample": "SpMM d=64 whole graph (all threads, with the reference's layout copies); SDDMM d=64 "
@@ -488,6 +515,9 @@ def _install_build_cache(spmm, sddmm):
 
 if __name__ == "__main__":
     a = parse_args()
+    if a.dims is None:
+        a.dims = "128" if a.workload == "C4" else "32,64,128,256,512"
+    WORKLOAD = a.workload
     if a.impl == "reference":
         run_reference_arm(a)
     else:
