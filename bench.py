@@ -69,7 +69,6 @@ def parse_args():
     p.add_argument("--shrink", type=int, default=1, help="divide node count (debug / profiling runs)")
     p.add_argument("--feat-tile", type=int, default=0)
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--no-nccl-register", action="store_true", help="plain tensors as all-gather buffers")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--e2e-steps", type=int, default=2)
     return p.parse_args()
@@ -290,9 +289,6 @@ def run_ours(args):
     local_nnz = local_adj.nnz
     log("[rank %d] rows [%d,%d) nnz %d built in %.1fs" % (rank, lo, hi, local_nnz, time.time() - t0))
 
-    if args.no_nccl_register:
-        import featgraph_b200.sharded as _sh
-        _sh.REGISTER_GATHER_BUFFERS = False
     spmm = ShardedSpMM(local_adj, bounds, device=device)
     sddmm = ShardedSDDMM(local_adj, bounds, device=device)
 

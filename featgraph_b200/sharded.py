@@ -103,31 +103,6 @@ def all_gather_padded(padded, local, bounds, group=None):
     return padded
 
 
-# Allocate the gather buffers from NCCL's own allocator and register them with the communicator, so
-# that the all-gather can run zero-copy through NVSwitch multicast (NVLS) where the fabric has it.
-# Falls back to an ordinary tensor when the torch / NCCL build lacks the hooks.
-REGISTER_GATHER_BUFFERS = True
-_registered_pools = []  # kept alive for the life of the process
-
-
-def gather_buffer(shape, device, group=None):
-    """Zero-filled float32 device tensor to all-gather into."""
-    if REGISTER_GATHER_BUFFERS and dist.is_initialized() and dist.get_backend(group) == "nccl":
-        try:
-            pg = group if group is not None else dist.distributed_c10d._get_default_group()
-            backend = pg._get_backend(torch.device(device))
-            pool = torch.cuda.MemPool(backend.mem_allocator)
-            with torch.cuda.use_mem_pool(pool):
-                buf = torch.zeros(shape, dtype=torch.float32, device=device)
-            backend.register_mem_pool(pool)
-            _registered_pools.append(pool)
-            return buf
-        except Exception as exc:  # noqa: BLE001 - any failure here only costs speed
-            import warnings
-            warnings.warn("NCCL buffer registration unavailable (%s); using a plain tensor" % (exc,))
-    return torch.zeros(shape, dtype=torch.float32, device=device)
-
-
 class _ShardedBase:
     def __init__(self, bounds, group, device):
         self.group = group
@@ -163,7 +138,7 @@ class ShardedSpMM(_ShardedBase):
     def build(self, feat_len, feat_tile=0):
         from .placeholder import placeholder
         self.module.build([placeholder((self.n, feat_len))], {}, {"feat_tile": feat_tile})
-        self.x_full = gather_buffer((self.n, feat_len), self.device, self.group)
+        self.x_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, x_local):
         """The exchange step alone: every rank's feature rows into this rank's ``x_full``."""
@@ -194,7 +169,7 @@ class ShardedSDDMM(_ShardedBase):
     def build(self, feat_len):
         from .placeholder import placeholder
         self.module.build([placeholder((self.n, feat_len)), placeholder((self.row_hi - self.row_lo, feat_len))], {}, {})
-        self.src_full = gather_buffer((self.n, feat_len), self.device, self.group)
+        self.src_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, src_local):
         return self._gather(self.src_full, src_local)
