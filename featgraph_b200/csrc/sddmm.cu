@@ -59,7 +59,7 @@ struct SddmmArgs {
 // CACHE_DST: edge list is row-sorted, keep the row-side slice in registers.
 // MASKED: the tile is narrower than 4*G*NV floats (ragged last tile).
 template <int G, int NV, int U, bool CACHE_DST, bool MASKED>
-__global__ void __launch_bounds__(kThreads, NV >= 2 ? 2 : 4) sddmm_tile_kernel(const SddmmArgs a) {
+__global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_tile_kernel(const SddmmArgs a) {
     static_assert(G % U == 0, "U must divide G");
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
@@ -267,7 +267,7 @@ int launch_width(const SddmmArgs& a, bool cache, unsigned blocks, cudaStream_t s
     if (q <= 2) FG_SDDMM(2, 1, 2);
     if (q <= 4) FG_SDDMM(4, 1, 4);
     if (q <= 8) FG_SDDMM(8, 1, 8);
-    if (q <= 16) FG_SDDMM(16, 1, 8);
+    if (q <= 16) FG_SDDMM(8, 2, 4);  // 64-float tiles: 4 edges per warp step measured fastest
     if (q <= 32) FG_SDDMM(32, 1, 8);
     if (q <= 64) FG_SDDMM(32, 2, 4);
     if (q <= 96) FG_SDDMM(32, 3, 2);
