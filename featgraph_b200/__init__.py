@@ -13,3 +13,13 @@ def __getattr__(name):
         import importlib
         return importlib.import_module("." + name, __name__)
     raise AttributeError(name)
+
+
+def host_sync(device=None):
+    """Wait for every ``run_host(..., wait=False)`` call issued by this thread."""
+    import ctypes
+    import torch
+    from . import _native
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _native.check(_native.lib().fg_host_sync(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))

@@ -35,7 +35,9 @@ struct Pipeline {
         }
         if (!in) FG_CUDA_TRY(cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking));
         if (!out) FG_CUDA_TRY(cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking));
-        next = 0;
+        // events are handed out round robin; 512 in rotation is far more than the calls that can be
+        // in flight between two host synchronisations need (two per column window)
+        if (next >= 512) next = 0;
         return FG_OK;
     }
     int event(cudaEvent_t* e) {
@@ -83,7 +85,7 @@ extern "C" {
 int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indptr,
                          const int32_t* d_indices, const float* d_vals, const float* h_x, float* h_out,
                          float* d_x_staging, float* d_out_staging, int64_t n_rows, int64_t n_cols,
-                         int64_t nnz, int32_t d, int32_t chunk, void* stream) {
+                         int64_t nnz, int32_t d, int32_t chunk, int32_t flags, void* stream) {
     if (d < 1 || n_rows < 0 || n_cols < 0)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld d=%d", (long long)n_rows,
                         (long long)n_cols, d);
@@ -95,11 +97,14 @@ int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indpt
     Pipeline& p = pipeline();
     FG_TRY_RC(p.prepare());
     const int w = window_width(d, chunk);
-    cudaEvent_t start;
-    FG_TRY_RC(p.event(&start));
-    FG_CUDA_TRY(cudaEventRecord(start, s));  // staging buffers may still be in use on the caller's stream
-    FG_CUDA_TRY(cudaStreamWaitEvent(p.in, start, 0));
-    FG_CUDA_TRY(cudaStreamWaitEvent(p.out, start, 0));
+    const bool deferred = (flags & FG_HOST_DEFERRED) != 0;
+    if (!deferred) {
+        cudaEvent_t start;
+        FG_TRY_RC(p.event(&start));
+        FG_CUDA_TRY(cudaEventRecord(start, s));  // staging buffers may still be in use on the caller's stream
+        FG_CUDA_TRY(cudaStreamWaitEvent(p.in, start, 0));
+        FG_CUDA_TRY(cudaStreamWaitEvent(p.out, start, 0));
+    }
     for (int c0 = 0; c0 < d; c0 += w) {
         const int wc = d - c0 < w ? d - c0 : w;
         cudaEvent_t in_done, k_done;
@@ -114,6 +119,7 @@ int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indpt
         FG_CUDA_TRY(cudaStreamWaitEvent(p.out, k_done, 0));
         FG_CUDA_TRY(copy_window(h_out, d_out_staging, n_rows, d, c0, wc, cudaMemcpyDeviceToHost, p.out));
     }
+    if (deferred) return FG_OK;
     FG_CUDA_TRY(cudaStreamSynchronize(p.out));
     FG_CUDA_TRY(cudaStreamSynchronize(s));
     return FG_OK;
@@ -122,7 +128,7 @@ int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indpt
 int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const float* h_src,
                           const float* h_dst, float* h_out, float* d_src_staging, float* d_dst_staging,
                           float* d_out_staging, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
-                          int32_t rows_sorted, int32_t chunk, void* stream) {
+                          int32_t rows_sorted, int32_t chunk, int32_t flags, void* stream) {
     if (d < 1 || n_rows < 0 || n_cols < 0 || nnz < 0)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d",
                         (long long)n_rows, (long long)n_cols, (long long)nnz, d);
@@ -134,10 +140,13 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
     Pipeline& p = pipeline();
     FG_TRY_RC(p.prepare());
     const int w = window_width(d, chunk);
-    cudaEvent_t start;
-    FG_TRY_RC(p.event(&start));
-    FG_CUDA_TRY(cudaEventRecord(start, s));
-    FG_CUDA_TRY(cudaStreamWaitEvent(p.in, start, 0));
+    const bool deferred = (flags & FG_HOST_DEFERRED) != 0;
+    if (!deferred) {
+        cudaEvent_t start;
+        FG_TRY_RC(p.event(&start));
+        FG_CUDA_TRY(cudaEventRecord(start, s));
+        FG_CUDA_TRY(cudaStreamWaitEvent(p.in, start, 0));
+    }
     for (int c0 = 0; c0 < d; c0 += w) {
         const int wc = d - c0 < w ? d - c0 : w;
         cudaEvent_t in_done;
@@ -149,8 +158,23 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
         FG_TRY_RC(fg_sddmm_coo_f32(d_row, d_col, d_src_staging + c0, d, d_dst_staging + c0, d, d_out_staging,
                                    n_rows, n_cols, nnz, wc, rows_sorted, c0 > 0 ? 1 : 0, 0, stream));
     }
-    FG_CUDA_TRY(cudaMemcpyAsync(h_out, d_out_staging, sizeof(float) * nnz, cudaMemcpyDeviceToHost, s));
+    // the result leaves on the copy-out stream, so that a following call's kernels need not wait for it
+    cudaEvent_t k_done;
+    FG_TRY_RC(p.event(&k_done));
+    FG_CUDA_TRY(cudaEventRecord(k_done, s));
+    FG_CUDA_TRY(cudaStreamWaitEvent(p.out, k_done, 0));
+    FG_CUDA_TRY(cudaMemcpyAsync(h_out, d_out_staging, sizeof(float) * nnz, cudaMemcpyDeviceToHost, p.out));
+    if (deferred) return FG_OK;
+    FG_CUDA_TRY(cudaStreamSynchronize(p.out));
     FG_CUDA_TRY(cudaStreamSynchronize(s));
+    return FG_OK;
+}
+
+int fg_host_sync(void* stream) {
+    Pipeline& p = pipeline();
+    if (p.in) FG_CUDA_TRY(cudaStreamSynchronize(p.in));
+    FG_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    if (p.out) FG_CUDA_TRY(cudaStreamSynchronize(p.out));
     return FG_OK;
 }
 

@@ -135,10 +135,12 @@ class SDDMMbase:
             self._launch(src, dst, self.out)
         return self.out
 
-    def run_host(self, inputs, out=None, chunk=0):
+    def run_host(self, inputs, out=None, chunk=0, wait=True):
         """Host-buffer call: both feature matrices in host memory (numpy or CPU tensors, float32,
         contiguous; pinned for full copy speed), per-edge result back in host memory, copies
-        pipelined against the kernels by ``fg_sddmm_coo_f32_host``.  Returns the host tensor."""
+        pipelined against the kernels by ``fg_sddmm_coo_f32_host``.  Returns the host tensor.
+        ``wait=False``: return at once; the tensor is complete after ``featgraph_b200.host_sync()``
+        (lets this call's copy-out overlap the next call; do not reuse this module before that)."""
         if self.out is None:
             raise RuntimeError("call build() before run_host()")
         ts = [torch.from_numpy(x) if isinstance(x, np.ndarray) else x for x in inputs]
@@ -160,7 +162,7 @@ class SDDMMbase:
                 dev.ptr(self._adj_row), dev.ptr(self._adj_col), ctypes.c_void_p(ts[0].data_ptr()),
                 ctypes.c_void_p(ts[1].data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(self._staging[0]),
                 dev.ptr(self._staging[1]), dev.ptr(self.out), self._num_rows, self._num_cols, self._nnz, d,
-                self._rows_sorted, int(chunk), dev.stream_ptr(self._device)))
+                self._rows_sorted, int(chunk), 0 if wait else 1, dev.stream_ptr(self._device)))
         return out
 
     def measure_average_time(self, inputs, num_runs):

@@ -159,11 +159,13 @@ class SpMMbase:
             self._launch(x, self.out)
         return self.out
 
-    def run_host(self, inputs, out=None, chunk=0):
+    def run_host(self, inputs, out=None, chunk=0, wait=True):
         """Host-buffer call: features in host memory (numpy array or CPU tensor, float32,
         contiguous; pinned memory gives full copy speed), result back in host memory.  Copies and
         kernels are pipelined over column windows by ``fg_spmm_csr_f32_host``.  ``out``: a CPU
-        float32 tensor ``[num_rows, feat_len]`` to fill (allocated pinned if omitted).  Returns it."""
+        float32 tensor ``[num_rows, feat_len]`` to fill (allocated pinned if omitted).  Returns it.
+        ``wait=False``: return at once; the tensor is complete after ``featgraph_b200.host_sync()``
+        (lets this call's copy-out overlap the next call; do not reuse this module before that)."""
         if self.out is None:
             raise RuntimeError("call build() before run_host()")
         (x,) = inputs
@@ -188,7 +190,7 @@ class SpMMbase:
                 self._schedule, dev.ptr(self._adj_pos), dev.ptr(self._adj_idx), dev.ptr(self._adj_vals),
                 ctypes.c_void_p(xt.data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(self._x_staging),
                 dev.ptr(self.out), self._num_rows, self._num_cols, self._nnz, d, int(chunk),
-                dev.stream_ptr(self._device)))
+                0 if wait else 1, dev.stream_ptr(self._device)))
         return out
 
     def measure_average_time(self, inputs, num_runs):

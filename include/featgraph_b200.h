@@ -173,15 +173,24 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
  * is allocated.  Pinned host memory gives full copy speed, pageable memory works.  The call
  * returns when the host result is complete (it synchronises `stream`).  Values: SpMM as
  * fg_spmm_csr_f32; SDDMM as fg_sddmm_coo_f32 with feat_tile = chunk.
+ *   flags  0, or FG_HOST_DEFERRED: enqueue everything and return at once; the host result is
+ *          complete after fg_host_sync(stream) on the same host thread.  Deferred calls let the
+ *          copy-out of one call overlap the copy-in and kernels of the next.  The caller promises
+ *          that the staging buffers of a deferred call are not touched by anything else (another
+ *          call with the same buffers included) until that fg_host_sync.
  * -------------------------------------------------------------------------------------- */
+#define FG_HOST_DEFERRED 1
 int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indptr,
                          const int32_t* d_indices, const float* d_vals, const float* h_x, float* h_out,
                          float* d_x_staging, float* d_out_staging, int64_t n_rows, int64_t n_cols,
-                         int64_t nnz, int32_t d, int32_t chunk, void* stream);
+                         int64_t nnz, int32_t d, int32_t chunk, int32_t flags, void* stream);
 int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const float* h_src,
                           const float* h_dst, float* h_out, float* d_src_staging, float* d_dst_staging,
                           float* d_out_staging, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
-                          int32_t rows_sorted, int32_t chunk, void* stream);
+                          int32_t rows_sorted, int32_t chunk, int32_t flags, void* stream);
+/* Wait until every host-buffer call issued by this host thread (on `stream` and on the library's
+ * copy streams) has finished. */
+int fg_host_sync(void* stream);
 
 /* --------------------------------------------------------------------------------------
  * Index checks (the code generator of the reference emits shape asserts only; these add

@@ -94,6 +94,16 @@ def test_host_buffer_calls_pipeline_windows_and_match_device_calls(oracle, d, ch
     np.testing.assert_allclose(e, oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)
     with pytest.raises(ValueError):
         sp_.run_host([x[:, :8].copy()])
+    # deferred completion: both calls are only enqueued; results are complete after host_sync()
+    import featgraph_b200
+    o1 = torch.zeros((n, d)).pin_memory()
+    o2 = torch.zeros((coo.nnz,)).pin_memory()
+    xp, yp = torch.from_numpy(x).pin_memory(), torch.from_numpy(y).pin_memory()
+    sp_.run_host([xp], out=o1, chunk=chunk, wait=False)
+    sd.run_host([xp, yp], out=o2, chunk=chunk, wait=False)
+    featgraph_b200.host_sync()
+    np.testing.assert_array_equal(o1.numpy(), want)
+    np.testing.assert_allclose(o2.numpy(), oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)
 
 
 def test_spmm_build_and_run_argument_errors(adj_csr):
