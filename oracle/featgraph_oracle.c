@@ -6,13 +6,18 @@
  * the smoke test and the benchmark's CPU-baseline leg compare against or time.
  * Nothing the library ships calls it, links it or falls back to it.
  *
- * PARITY UNPINNED for floating point: the reference executes these loops through a
- * third-party code generator (Apache TVM, not vendored, version not pinned by the
- * reference) that is not available, and the reference's own tests hold no numeric
- * golden vectors for SpMM/SDDMM (they compare random inputs with scipy/numpy at
+ * PARITY STATUS.  The reference executes these loops through a third-party code generator
+ * (Apache TVM, not vendored, version not pinned by the reference), and its own tests hold no
+ * numeric golden vectors for SpMM/SDDMM (they compare random inputs with scipy/numpy at
  * rtol = atol = 1e-4: tests/test_module_spmm.py:29-30, tests/test_module_sddmm.py:34-37).
- * What is pinned: loop order, accumulation order and index arithmetic, restated
- * from the cited lines; and agreement with scipy/numpy on the reference's test shapes.
+ *  - SDDMM: PINNED.  The reference's own compute definition (op/vanilla_sddmm.py:6-63), lowered
+ *    and compiled by a TVM build (the 0.23.dev0 fork shipped inside the tilelang package, C
+ *    backend), gives bit-identical output to fgo_sddmm_x86 with use_fma = 0 on every committed
+ *    case (tests/golden/sddmm_reference_tvm.npz, made by make_sddmm_reference_golden.py).
+ *  - SpMM: PARITY UNPINNED.  The reference's SpMM definitions do not lower in that TVM fork
+ *    (data-dependent reduce extent).  Pinned instead: loop order, accumulation order and index
+ *    arithmetic restated from the cited lines, and bit-equality with scipy's CSR product on
+ *    the reference's test shape (scipy is what the reference's tests compare against).
  *
  * Arithmetic model: fp32 throughout, one rounding for the product and one for the
  * sum (no fused multiply-add): the reference's x86 target string is the bare

@@ -47,3 +47,18 @@ def reference_util_or_skip():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
+
+
+def sddmm_reference_cases():
+    """(name, row, col, src, dst, num_feat_partitions, reference_output) for every case of
+    tests/golden/sddmm_reference_tvm.npz (outputs of the reference's own SDDMM definition compiled by a
+    TVM build; inputs are re-created from their seeds by the generating script's own functions)."""
+    import importlib.util
+    path = os.path.join(GOLDEN, "make_sddmm_reference_golden.py")
+    spec = importlib.util.spec_from_file_location("make_sddmm_reference_golden", path)
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    fixture = np.load(os.path.join(GOLDEN, "sddmm_reference_tvm.npz"))
+    for name, n_rows, n_cols, d, nfp, seed in gen.cases():
+        row, col, src, dst = gen.inputs(n_rows, n_cols, d, seed)
+        yield name, row, col, src, dst, nfp, fixture[name]

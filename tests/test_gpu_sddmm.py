@@ -21,6 +21,17 @@ def test_reference_test_shape_fixture(oracle, numeric_golden):
     np.testing.assert_allclose(g["sddmm_numpy"], out, rtol=1e-4, atol=1e-4)  # the reference's own check
 
 
+def test_against_the_references_own_definition_compiled_by_tvm():
+    """GPU results against outputs of the reference's SDDMM definition run through a TVM build
+    (tests/golden/sddmm_reference_tvm.npz), at the stated tolerance."""
+    import gpu_util as G
+    from conftest import sddmm_reference_cases
+    for name, row, col, src, dst, nfp, ref_out in sddmm_reference_cases():
+        for tile in (0, 32):
+            np.testing.assert_allclose(G.sddmm(row, col, src, dst, feat_tile=tile), ref_out, rtol=RTOL, atol=ATOL,
+                                       err_msg=name)
+
+
 @pytest.mark.parametrize("d", [1, 3, 4, 8, 20, 32, 33, 48, 64, 100, 128, 200, 256, 384, 512, 640])
 @pytest.mark.parametrize("order", ["csr", "shuffled"])
 def test_feature_lengths_and_edge_orders(oracle, d, order):

@@ -52,6 +52,20 @@ def test_sddmm_oracle_vs_numpy_fixture(oracle, numeric_golden):
     np.testing.assert_array_equal(out, oracle.sddmm(g["coo_row"], g["coo_col"], g["x"], g["y"], threads=4))
 
 
+def test_sddmm_oracle_equals_the_references_own_definition_compiled_by_tvm(oracle):
+    """The pin for SDDMM: the reference's compute definition (op/vanilla_sddmm.py:6-63), lowered and
+    compiled by a TVM build, gives exactly the oracle's bits - with separate product and sum
+    roundings, not with fused ones."""
+    from conftest import sddmm_reference_cases
+    n = 0
+    for name, row, col, src, dst, nfp, ref_out in sddmm_reference_cases():
+        got = oracle.sddmm(row, col, src, dst, num_feat_partitions=nfp)
+        np.testing.assert_array_equal(got, ref_out, err_msg=name)
+        assert not np.array_equal(oracle.sddmm(row, col, src, dst, use_fma=True), ref_out), name
+        n += 1
+    assert n == 4
+
+
 def test_sddmm_oracle_with_2d_partition(oracle, numeric_golden):
     g = numeric_golden
     coo = sp.coo_matrix((np.ones(len(g["coo_row"]), np.int32), (g["coo_row"], g["coo_col"])), shape=(127, 255))
