@@ -162,6 +162,15 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
                      int64_t nnz, int32_t d, int32_t rows_sorted, int32_t accumulate, int32_t feat_tile,
                      void* stream);
 
+/* SDDMM with the reference's x86 summation order, bit for bit: every product and every sum
+ * rounded separately, k strictly ascending (python/featgraph/op/vanilla_sddmm.py:43-62 with the
+ * loop order of :66-74).  Same arrays and strides as fg_sddmm_coo_f32; accumulate != 0 continues
+ * the sequential sum from what out holds (column windows in ascending order then still give the
+ * sequential sum over all columns).  About half the speed of fg_sddmm_coo_f32. */
+int fg_sddmm_coo_f32_exact(const int32_t* d_row, const int32_t* d_col, const float* d_src, int64_t ld_src,
+                           const float* d_dst, int64_t ld_dst, float* d_out, int64_t n_rows, int64_t n_cols,
+                           int64_t nnz, int32_t d, int32_t accumulate, void* stream);
+
 /* --------------------------------------------------------------------------------------
  * Host-buffer calls: features in HOST memory (h_*), results back to HOST memory, adjacency
  * already on the device.  They replace the three steps a caller of the reference performs

@@ -92,3 +92,16 @@ def sddmm(row, col, src, dst, rows_sorted=0, feat_tile=0):
     torch.cuda.synchronize()
     assert guards_intact(buf), "kernel wrote outside its output"
     return out.cpu().numpy()
+
+
+def sddmm_exact(row, col, src, dst):
+    L = _native.lib()
+    n_cols, d = src.shape
+    n_rows = dst.shape[0]
+    rr, cc, ss, dd = dev(row, np.int32), dev(col, np.int32), dev(src, np.float32), dev(dst, np.float32)
+    buf, out = guarded(len(row))
+    _native.check(L.fg_sddmm_coo_f32_exact(p(rr), p(cc), p(ss), 0, p(dd), 0, p(out), n_rows, n_cols, len(row), d, 0,
+                                           stream()))
+    torch.cuda.synchronize()
+    assert guards_intact(buf), "kernel wrote outside its output"
+    return out.cpu().numpy()

@@ -60,6 +60,38 @@ def test_feature_tiles_accumulate_to_the_same_dot_product(oracle, d, tile):
                                    rtol=RTOL, atol=ATOL)
 
 
+@pytest.mark.parametrize("d", [1, 3, 4, 31, 32, 33, 36, 64, 100, 128, 200, 512])
+def test_exact_order_kernel_is_bit_identical_to_the_oracle(oracle, d):
+    import gpu_util as G
+    coo = sp.random(127, 255, density=0.1, format="coo", random_state=d)  # unsorted edge list
+    row, col = coo.row.astype(np.int32), coo.col.astype(np.int32)
+    src, dst = _feat(255, d, 5), _feat(127, d, 6)
+    np.testing.assert_array_equal(G.sddmm_exact(row, col, src, dst), oracle.sddmm(row, col, src, dst))
+    for nnz in (0, 1, 33, 2049):
+        np.testing.assert_array_equal(G.sddmm_exact(row[:nnz], col[:nnz], src, dst),
+                                      oracle.sddmm(row[:nnz], col[:nnz], src, dst))
+
+
+def test_exact_order_kernel_reproduces_the_references_tvm_output_bit_for_bit():
+    """The committed outputs of the reference's own SDDMM definition (compiled by a TVM build)."""
+    import gpu_util as G
+    from conftest import sddmm_reference_cases
+    for name, row, col, src, dst, nfp, ref_out in sddmm_reference_cases():
+        np.testing.assert_array_equal(G.sddmm_exact(row, col, src, dst), ref_out, err_msg=name)
+
+
+def test_exact_option_of_the_module(oracle, numeric_golden):
+    import torch
+    from featgraph import placeholder
+    from featgraph.module import VanillaSDDMMcuda
+    g = numeric_golden
+    coo = sp.coo_matrix((np.ones(len(g["coo_row"]), np.int32), (g["coo_row"], g["coo_col"])), shape=(127, 255))
+    m = VanillaSDDMMcuda(coo)
+    m.build([placeholder((255, 128)), placeholder((127, 128))], {}, {"exact": True})
+    out = m.run([torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["y"]).cuda()]).cpu().numpy()
+    np.testing.assert_array_equal(out, oracle.sddmm(g["coo_row"], g["coo_col"], g["x"], g["y"]))
+
+
 def test_exact_on_small_integers():
     """Integer-valued features make every fp32 operation exact, whatever the summation tree."""
     import gpu_util as G
