@@ -249,8 +249,9 @@ sddmm_generic_kernel(const int32_t* __restrict__ row, const int32_t* __restrict_
 // rows in shared memory: eight 128-bit loads per matrix (4 edges per load, 8 lanes x 16 bytes per
 // edge) are stored k-major with a rotation, tile[k][(edge + k) % 32], which makes both the
 // scattered stores and the per-lane reads tile[k][(lane + k) % 32] bank-conflict free.
-// About half the speed of sddmm_tile_kernel (every float crosses shared memory twice and the
-// per-edge sum is a serial chain); an opt-in for callers that want bit-for-bit agreement.
+// Three to four times slower than sddmm_tile_kernel (both rows of every edge cross shared memory
+// twice and the per-edge sum is a serial chain); an opt-in for callers that want bit-for-bit
+// agreement.
 // ---------------------------------------------------------------------------------------------
 constexpr int kExactWarps = 4;  // 32 KB of static shared memory per block
 
@@ -462,10 +463,22 @@ int fg_sddmm_coo_f32_exact(const int32_t* d_row, const int32_t* d_col, const flo
     const int64_t nblocks = (nnz + edges_per_block - 1) / edges_per_block;
     if (nblocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
     const bool vec = (ld_src % 4 == 0) && (ld_dst % 4 == 0) && fg::aligned16(d_src) && fg::aligned16(d_dst);
-    sddmm_exact_kernel<<<(unsigned)nblocks, kExactWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        d_row, d_col, d_src, (int)ld_src, d_dst, (int)ld_dst, d_out, nnz, d, accumulate, vec);
+    // Column windows keep the gathered slice of src in L2, as in fg_sddmm_coo_f32; a window continues
+    // the sequential sum from out[e], so the k order - and every bit - is that of a single pass.
+    int tile = d;
+    const int64_t l2 = l2_size_bytes();
+    if (n_cols * (int64_t)d * 4 > l2 - l2 / 4 && n_cols * 32 * 4 <= l2 / 2) {
+        tile = 32;
+        while (tile * 2 < d && n_cols * (int64_t)(tile * 2) * 4 <= l2 / 2) tile *= 2;
+    }
+    for (int f0 = 0; f0 < d; f0 += tile) {
+        const int wd = d - f0 < tile ? d - f0 : tile;
+        sddmm_exact_kernel<<<(unsigned)nblocks, kExactWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+            d_row, d_col, d_src + f0, (int)ld_src, d_dst + f0, (int)ld_dst, d_out, nnz, wd,
+            (f0 > 0 || accumulate) ? 1 : 0, vec);
+        fg::count_launches(1);
+    }
     FG_CUDA_TRY(cudaGetLastError());
-    fg::count_launches(1);
     return FG_OK;
 }
 

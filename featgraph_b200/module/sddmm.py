@@ -104,7 +104,7 @@ class SDDMMbase:
     def build(self, input_placeholders, compute_args, schedule_args):
         """Fix the feature shapes and allocate the (reused) per-edge output (reference :72-92).
         ``schedule_args['exact'] = True`` selects the kernel that sums every dot product in the x86
-        loop's order (bit-identical to it, about half as fast); ``feat_tile`` sets the L2 tile width."""
+        loop's order (bit-identical to it, three to four times slower); ``feat_tile`` sets the L2 tile width."""
         src_shape, dst_shape, _, _ = self._plan(input_placeholders, compute_args, schedule_args)
         self._shapes = (src_shape, dst_shape)
         self._feat_tile = self._planned_tile

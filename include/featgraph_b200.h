@@ -166,7 +166,7 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
  * rounded separately, k strictly ascending (python/featgraph/op/vanilla_sddmm.py:43-62 with the
  * loop order of :66-74).  Same arrays and strides as fg_sddmm_coo_f32; accumulate != 0 continues
  * the sequential sum from what out holds (column windows in ascending order then still give the
- * sequential sum over all columns).  About half the speed of fg_sddmm_coo_f32. */
+ * sequential sum over all columns).  Three to four times slower than fg_sddmm_coo_f32. */
 int fg_sddmm_coo_f32_exact(const int32_t* d_row, const int32_t* d_col, const float* d_src, int64_t ld_src,
                            const float* d_dst, int64_t ld_dst, float* d_out, int64_t n_rows, int64_t n_cols,
                            int64_t nnz, int32_t d, int32_t accumulate, void* stream);

@@ -105,6 +105,24 @@ def test_c2_full_size_sddmm(oracle, c2_graph):
     np.testing.assert_array_equal(out4, 4.0 * tiled)
 
 
+def test_c2_full_size_sddmm_exact_order(oracle, c2_graph):
+    """d = 128 on the full graph: the exact-order kernel runs in two 64-float column windows here
+    (the second continues the first one's sequential sum) and still equals the oracle bit for bit."""
+    from featgraph_b200 import graphgen
+    adj = c2_graph
+    n = adj.shape[0]
+    src = graphgen.workload_features("C2", n, 128, 0)
+    dst = graphgen.workload_features("C2", n, 128, 1)
+    m = VanillaSDDMMcuda(adj.tocoo())
+    m.build([placeholder((n, 128)), placeholder((n, 128))], {}, {"exact": True})
+    out_e = m.run([torch.from_numpy(src).to(m.ctx), torch.from_numpy(dst).to(m.ctx)]).cpu().numpy()
+    deg = np.diff(adj.indptr)
+    rows = np.unique(np.concatenate([np.random.default_rng(7).integers(0, n, 200), np.argsort(-deg)[:2]]))
+    _, cols, _, idx = _sub_csr(adj, rows)
+    row_of = np.repeat(rows, deg[rows]).astype(np.int32)
+    np.testing.assert_array_equal(out_e[idx], oracle.sddmm(row_of, cols, src, dst))
+
+
 def test_c2_full_size_shard_boundaries(c2_graph):
     """nnz-balanced row ranges at 1/2/4/8 parts: exact searchsorted definition, nothing lost, balance
     within one maximal row."""
