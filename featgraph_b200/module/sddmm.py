@@ -2,8 +2,9 @@
 reference, executed by hand-written sm_100a kernels through the C ABI.
 
 Both classes run on the GPU.  ``VanillaSDDMMx86`` keeps the x86 class's 2-D partitioning
-knobs (the edge list is regrouped tile by tile and ``edge_mapping`` undoes it);
-``VanillaSDDMMcuda`` takes the edge list as given.
+knobs (the edge list is regrouped tile by tile and ``edge_mapping`` undoes it) and its summation
+order (bit-identical results); ``VanillaSDDMMcuda`` takes the edge list as given and sums each
+dot product as a tree, as the reference's CUDA schedule does.
 """
 import numpy as np
 import torch
@@ -18,6 +19,7 @@ class SDDMMbase:
 
     _compute_keys = ()
     _schedule_keys = ()
+    _exact_by_default = False
 
     def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device=None):
         # COO in SDDMM-like kernels (reference :28-31)
@@ -95,7 +97,7 @@ class SDDMMbase:
             if 4 <= f <= 512 and (f & (f - 1)) == 0:
                 tile = f
         self._planned_tile = tile
-        self._planned_exact = bool(schedule_args.get("exact", False))
+        self._planned_exact = bool(schedule_args.get("exact", self._exact_by_default))
         return src_shape, dst_shape, d, nfp
 
     def _check_schedule(self, schedule_args, nfp):
@@ -201,9 +203,12 @@ class SDDMMbase:
 
 
 class VanillaSDDMMx86(SDDMMbase):
-    """The x86 class of the reference (python/featgraph/module/sddmm.py:168-176)."""
+    """The x86 class of the reference (python/featgraph/module/sddmm.py:168-176).  It keeps the x86
+    path's arithmetic: by default the exact-order kernel runs, so results are bit-identical to the
+    x86 loop (``schedule_args={'exact': False}`` selects the faster tree-summed kernel)."""
 
     _compute_keys = ("num_feat_partitions",)
+    _exact_by_default = True
     _schedule_keys = ("num_feat_partitions", "feat_tile", "exact")
 
     def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device=None):
