@@ -59,6 +59,11 @@ def all_gather_rows(full, local, bounds, group=None):
     return full
 
 
+class ExchangeError(RuntimeError):
+    """The feature all-gather failed or timed out (a peer rank is gone or stuck).  Raised on the host;
+    nothing is left running on the GPU by this layer, and the local modules stay usable."""
+
+
 def padded_layout(bounds):
     """Equal-sized slots for an all-gather of unequal row blocks: rank p's rows sit at
     ``[p*slot, p*slot + rows_p)`` of a ``world*slot``-row buffer.  Returns ``(slot, shift)`` with
@@ -96,10 +101,13 @@ def all_gather_padded(padded, local, bounds, group=None):
     mine = padded[rank * slot:(rank + 1) * slot]
     mine[:rows].copy_(local)
     if world > 1:
-        if dist.get_backend(group) == "nccl":
-            dist.all_gather_into_tensor(padded, mine, group=group)
-        else:
-            dist.all_gather([padded[p * slot:(p + 1) * slot] for p in range(world)], mine.clone(), group=group)
+        try:
+            if dist.get_backend(group) == "nccl":
+                dist.all_gather_into_tensor(padded, mine, group=group)
+            else:
+                dist.all_gather([padded[p * slot:(p + 1) * slot] for p in range(world)], mine.clone(), group=group)
+        except Exception as exc:  # the process group's timeout, a closed connection, an aborted communicator
+            raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (rank, world, exc)) from exc
     return padded
 
 

@@ -99,3 +99,45 @@ def test_sharding_and_gather_on_cpu_ranks(tmp_path, world):
     build.build_graphgen()
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok%d" % r for r in range(world)]
+
+
+def _worker_peer_leaves(rank, world, port, tmpdir):
+    """Rank 1 leaves between steps (no collective in flight); rank 0's next exchange must end with an
+    ExchangeError within the process group's timeout instead of hanging."""
+    import datetime
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from featgraph_b200.sharded import ExchangeError, all_gather_padded, padded_layout
+    bounds = np.array([0, 5, 9])
+    slot, _ = padded_layout(bounds)
+    local = torch.full((int(bounds[rank + 1] - bounds[rank]), 4), float(rank))
+    padded = torch.zeros((world * slot, 4))
+    all_gather_padded(padded, local, bounds)  # step 1: everybody is there
+    assert padded[slot, 0] == 1.0 and padded[0, 0] == 0.0
+    if rank == 1:
+        open(os.path.join(tmpdir, "left"), "w").write("1")
+        os._exit(0)  # gone before step 2
+    t0 = time.time()
+    try:
+        all_gather_padded(padded, local, bounds)
+    except ExchangeError as exc:
+        assert "all-gather failed" in str(exc)
+        open(os.path.join(tmpdir, "detected"), "w").write("%.1f" % (time.time() - t0))
+    os._exit(0)  # skip the group's teardown: the peer is gone
+
+
+def test_a_missing_peer_is_reported_not_waited_for_forever(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_peer_leaves, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert not p.is_alive()
+    assert os.path.exists(os.path.join(tmp_path, "left"))
+    assert os.path.exists(os.path.join(tmp_path, "detected")), "rank 0 did not see an ExchangeError"
+    assert float(open(os.path.join(tmp_path, "detected")).read()) < 60
