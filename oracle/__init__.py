@@ -5,9 +5,10 @@ Python face of ``featgraph_oracle.c``: loads ``oracle/_ref/libfeatgraph_oracle.s
 each function for numpy arrays.  Only the tests, the smoke check and the benchmark's
 CPU-baseline leg import this package; the shipped library never does.
 
-Floating-point parity with the reference's generated x86 code is UNPINNED (see the
-header of ``featgraph_oracle.c``); index arithmetic and accumulation order follow
-python/featgraph/op/vanilla_spmm.py:41-62,195-224 and op/vanilla_sddmm.py:43-62.
+Parity: bit-identical to the reference's own SpMM / SDDMM compute definitions compiled by a TVM
+build (fixtures tests/golden/*_reference_tvm.npz; see the header of ``featgraph_oracle.c``);
+index arithmetic and accumulation order follow python/featgraph/op/vanilla_spmm.py:41-62,195-224
+and op/vanilla_sddmm.py:43-62.
 """
 import ctypes
 import os

@@ -14,10 +14,15 @@
  *    and compiled by a TVM build (the 0.23.dev0 fork shipped inside the tilelang package, C
  *    backend), gives bit-identical output to fgo_sddmm_x86 with use_fma = 0 on every committed
  *    case (tests/golden/sddmm_reference_tvm.npz, made by make_sddmm_reference_golden.py).
- *  - SpMM: PARITY UNPINNED.  The reference's SpMM definitions do not lower in that TVM fork
- *    (data-dependent reduce extent).  Pinned instead: loop order, accumulation order and index
- *    arithmetic restated from the cited lines, and bit-equality with scipy's CSR product on
- *    the reference's test shape (scipy is what the reference's tests compare against).
+ *  - SpMM (CSR x86, CSR CUDA and DDS definitions, op/vanilla_spmm.py:6-62, 83-125, 149-224):
+ *    PINNED the same way, on random non-unit values: fgo_spmm_csr_x86 / fgo_spmm_dds_x86 with
+ *    use_fma = 0 are bit-identical to the TVM-compiled outputs in
+ *    tests/golden/spmm_reference_tvm.npz (make_spmm_reference_golden.py; that script repairs one
+ *    lowering artefact of the fork - a tensor-expression load left in a loop extent - and touches
+ *    neither arithmetic nor loop order).  Also bit-equal to scipy's CSR product on the
+ *    reference's test shape (scipy is what the reference's tests compare against).
+ *    What the pin does not cover: the exact TVM release and LLVM backend the reference was run
+ *    with (unpinned by the reference itself); the fixtures come from that fork's C backend.
  *
  * Arithmetic model: fp32 throughout, one rounding for the product and one for the
  * sum (no fused multiply-add): the reference's x86 target string is the bare

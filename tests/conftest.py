@@ -62,3 +62,18 @@ def sddmm_reference_cases():
     for name, n_rows, n_cols, d, nfp, seed in gen.cases():
         row, col, src, dst = gen.inputs(n_rows, n_cols, d, seed)
         yield name, row, col, src, dst, nfp, fixture[name]
+
+
+def spmm_reference_cases():
+    """(name, kind, adj, x, num_feat_partitions, num_col_partitions, reference_output) for every case of
+    tests/golden/spmm_reference_tvm.npz (outputs of the reference's own SpMM definitions compiled by a TVM
+    build; inputs are re-created from their seeds by the generating script's own functions)."""
+    import importlib.util
+    path = os.path.join(GOLDEN, "make_spmm_reference_golden.py")
+    spec = importlib.util.spec_from_file_location("make_spmm_reference_golden", path)
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    fixture = np.load(os.path.join(GOLDEN, "spmm_reference_tvm.npz"))
+    for name, n_rows, n_cols, d, kind, nfp, ncp, seed, density in gen.cases():
+        adj, x = gen.inputs(n_rows, n_cols, d, seed, density)
+        yield name, kind, adj, x, nfp, ncp, fixture[name]

@@ -27,6 +27,21 @@ def test_reference_test_shape_fixture(oracle, numeric_golden):
     np.testing.assert_allclose(g["spmm_scipy"], out, rtol=1e-4, atol=1e-4)  # the reference's own check
 
 
+def test_bit_identical_to_the_references_own_definitions_compiled_by_tvm():
+    """GPU results against the committed outputs of the reference's SpMM definitions run through a TVM
+    build (tests/golden/spmm_reference_tvm.npz): CSR and DDS, random non-unit values, bit for bit."""
+    import gpu_util as G
+    from conftest import spmm_reference_cases
+    from featgraph_b200.util import util_convert_csr_to_dds
+    for name, kind, adj, x, nfp, ncp, ref_out in spmm_reference_cases():
+        if kind == "dds_x86":
+            s1_pos, s1_idx, vals = util_convert_csr_to_dds(adj, ncp)
+            got = G.spmm_dds(s1_pos, s1_idx, vals, x, adj.shape[0], ncp, indptr_for_schedule=adj.indptr)
+        else:
+            got = G.spmm_csr(adj.indptr, adj.indices, adj.data, x)
+        np.testing.assert_array_equal(got, ref_out, err_msg=name)
+
+
 @pytest.mark.parametrize("d", [1, 3, 4, 8, 20, 32, 33, 64, 100, 128, 256, 512])
 def test_feature_lengths(oracle, d):
     import gpu_util as G

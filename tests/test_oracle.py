@@ -52,6 +52,26 @@ def test_sddmm_oracle_vs_numpy_fixture(oracle, numeric_golden):
     np.testing.assert_array_equal(out, oracle.sddmm(g["coo_row"], g["coo_col"], g["x"], g["y"], threads=4))
 
 
+def test_spmm_oracle_equals_the_references_own_definitions_compiled_by_tvm(oracle):
+    """The pin for SpMM: the reference's CSR (x86 and CUDA) and DDS compute definitions
+    (op/vanilla_spmm.py:6-62, 83-125, 149-224), compiled by a TVM build, give exactly the oracle's bits
+    on random non-unit values - with separate product and sum roundings, not with fused ones."""
+    from conftest import spmm_reference_cases
+    n = 0
+    for name, kind, adj, x, nfp, ncp, ref_out in spmm_reference_cases():
+        if kind == "dds_x86":
+            dds = util_convert_csr_to_dds(adj, ncp)
+            got = oracle.spmm_dds(*dds, x, adj.shape[0], ncp, num_feat_partitions=nfp)
+            fused = oracle.spmm_dds(*dds, x, adj.shape[0], ncp, num_feat_partitions=nfp, use_fma=True)
+        else:
+            got = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x, num_feat_partitions=nfp, with_copies=True)
+            fused = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x, use_fma=True)
+        np.testing.assert_array_equal(got, ref_out, err_msg=name)
+        assert not np.array_equal(fused, ref_out), name
+        n += 1
+    assert n == 7
+
+
 def test_sddmm_oracle_equals_the_references_own_definition_compiled_by_tvm(oracle):
     """The pin for SDDMM: the reference's compute definition (op/vanilla_sddmm.py:6-63), lowered and
     compiled by a TVM build, gives exactly the oracle's bits - with separate product and sum
