@@ -505,10 +505,10 @@ def run_ours(args):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; keyed by (op, feature length).  Absent = not captured.
 NCU_TRAFFIC_BYTES = {
-    ("spmm", 512): 17.82e9,   # spmm_rows_kernel<16,4,0>, one launch (8 tiles inside)
-    ("spmm", 128): 4.72e9,
-    ("sddmm", 512): 25.9e9,   # sddmm_tile_kernel<16,1,8,1,0>: 8 tile launches of 3.24 GB each
-    ("sddmm", 128): 21.83e9,  # sddmm_tile_kernel<32,1,8,1,0>, single pass
+    ("spmm", 512): 12.17e9,   # spmm_rows_kernel<16,4,0,1>, one launch (8 tiles inside)
+    ("spmm", 128): 3.22e9,
+    ("sddmm", 512): 25.7e9,   # sddmm_tile_kernel<8,2,4,1,0>: 8 tile launches of 3.21 GB each
+    ("sddmm", 128): 7.58e9,   # two tile launches
 }
 
 
