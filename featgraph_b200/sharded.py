@@ -126,6 +126,25 @@ class _ShardedBase:
         return all_gather_padded(padded, local, self.bounds, self.group)
 
 
+class GatheredFeatures(_ShardedBase):
+    """A row-sharded feature matrix all-gathered ONCE into this rank's memory, for several ops to
+    read: SpMM and SDDMM of one GNN layer gather from the same matrix, and exchanging it per op
+    would double the NVLink traffic.  ``gather(x_local)`` returns ``self``; pass it to
+    ``ShardedSpMM.run`` / ``ShardedSDDMM.run`` in place of the local tensor."""
+
+    def __init__(self, bounds, feat_len, group=None, device=None):
+        super().__init__(bounds, group, device)
+        self.feat_len = int(feat_len)
+        self.full = torch.zeros((self.world * self.slot, self.feat_len), dtype=torch.float32, device=device)
+
+    def gather(self, x_local):
+        if self.world == 1:
+            self.full = x_local  # nothing to exchange: the local rows are all rows
+        else:
+            self._gather(self.full, x_local)
+        return self
+
+
 class ShardedSpMM(_ShardedBase):
     """Row-sharded SpMM for a square adjacency.
 
@@ -150,6 +169,9 @@ class ShardedSpMM(_ShardedBase):
 
     def gather(self, x_local):
         """The exchange step alone: every rank's feature rows into this rank's ``x_full``."""
+        if self.world == 1:
+            self.x_full = x_local
+            return x_local
         return self._gather(self.x_full, x_local)
 
     def compute(self):
@@ -157,7 +179,10 @@ class ShardedSpMM(_ShardedBase):
         return self.module.run([self.x_full])
 
     def run(self, x_local):
-        """x_local: this rank's rows of the feature matrix.  Returns this rank's rows of A.X."""
+        """x_local: this rank's rows of the feature matrix, or a ``GatheredFeatures`` that already
+        holds every rank's rows.  Returns this rank's rows of A.X."""
+        if isinstance(x_local, GatheredFeatures):
+            return self.module.run([x_local.full])
         self.gather(x_local)
         return self.compute()
 
@@ -180,13 +205,19 @@ class ShardedSDDMM(_ShardedBase):
         self.src_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, src_local):
+        if self.world == 1:
+            self.src_full = src_local
+            return src_local
         return self._gather(self.src_full, src_local)
 
     def compute(self, dst_local):
         return self.module.run([self.src_full, dst_local])
 
     def run(self, src_local, dst_local):
-        """src_local: this rank's rows of the column-side matrix (gathered from all ranks);
-        dst_local: this rank's rows of the row-side matrix.  Returns this rank's edges' dots."""
+        """src_local: this rank's rows of the column-side matrix (gathered from all ranks), or a
+        ``GatheredFeatures`` that already holds them; dst_local: this rank's rows of the row-side
+        matrix.  Returns this rank's edges' dots."""
+        if isinstance(src_local, GatheredFeatures):
+            return self.module.run([src_local.full, dst_local])
         self.gather(src_local)
         return self.compute(dst_local)

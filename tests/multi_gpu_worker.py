@@ -21,7 +21,7 @@ def main():
     world = dist.get_world_size()
     import oracle
     from featgraph_b200 import graphgen
-    from featgraph_b200.sharded import ShardedSDDMM, ShardedSpMM, shard_csr_rows
+    from featgraph_b200.sharded import GatheredFeatures, ShardedSDDMM, ShardedSpMM, shard_csr_rows
     from featgraph_b200.util import nnz_balanced_row_ranges
 
     n = 6000
@@ -44,6 +44,10 @@ def main():
             e = sddmm.run(xl, yl).cpu().numpy()
         want = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)[lo:hi]
         np.testing.assert_array_equal(out, want)
+        # one exchange shared by both ops
+        g = GatheredFeatures(bounds, d, device=device).gather(xl)
+        np.testing.assert_array_equal(spmm.run(g).cpu().numpy(), want)
+        np.testing.assert_array_equal(sddmm.run(g, yl).cpu().numpy(), e)
         want_e = oracle.sddmm(coo.row, coo.col, x, y)[adj.indptr[lo]:adj.indptr[hi]]
         np.testing.assert_allclose(e, want_e, rtol=1e-5, atol=1e-4)
     dist.barrier()
