@@ -69,6 +69,8 @@ def parse_args():
     p.add_argument("--shrink", type=int, default=1, help="divide node count (debug / profiling runs)")
     p.add_argument("--feat-tile", type=int, default=0)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-prefetch", action="store_true",
+                   help="N > 1: exchange each feature matrix right before its ops instead of during the previous ones")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--e2e-steps", type=int, default=2)
     return p.parse_args()
@@ -315,8 +317,12 @@ def run_ours(args):
     # d and shared (GatheredFeatures); C4: X feeds SpMM, Y feeds SDDMM - two exchanges.
     shared = {d: GatheredFeatures(bounds, d, device=device) for d in dims} if WORKLOAD != "C4" else {}
 
+    prefetch = world > 1 and WORKLOAD != "C4" and not args.no_prefetch
+
     def step(record=None):
-        for d in dims:
+        if prefetch:  # every feature matrix of the step is resident: exchange d[k+1] while d[k] computes
+            shared[dims[0]].gather_async(dev_feats[dims[0]][0])
+        for k, d in enumerate(dims):
             xd, yd = dev_feats[d]
             spmm.build_cached(d, args.feat_tile)
             sddmm.build_cached(d)
@@ -335,7 +341,12 @@ def run_ours(args):
                     ev[3].record(stream)
                 sddmm.compute(h)
             else:
-                g = shared[d].gather(xd)
+                if prefetch:
+                    if k + 1 < len(dims):
+                        shared[dims[k + 1]].gather_async(dev_feats[dims[k + 1]][0])
+                    g = shared[d].wait()
+                else:
+                    g = shared[d].gather(xd)
                 if ev:
                     ev[1].record(stream)
                 spmm.run(g)
@@ -493,7 +504,8 @@ def run_ours(args):
                                 if WORKLOAD == "C4" else
                                 "C2/C3 power-law graph %d nodes / %d edges: SpMM + SDDMM at each d") % (n, nnz),
                    "dims": dims, "parallelism": "row-sharded x%d (nnz-balanced); each feature matrix all-gathered "
-                   "once per step and d, inside the timed region" % world if world > 1 else "single GPU",
+                   "once per step and d, inside the timed region%s" % (world, ", the exchange for the next d running beside "
+                   "the current d's kernels" if prefetch else "") if world > 1 else "single GPU",
                    "l2_policy": "inputs larger than L2 (CSR arrays %.0f MB per pass; 10 different kernels "
                                 "and feature matrices between repeats of any one)" % (8.0 * nnz / 1e6),
                    "feat_tile": args.feat_tile or "auto"},

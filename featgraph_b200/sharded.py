@@ -144,6 +144,34 @@ class GatheredFeatures(_ShardedBase):
             self._gather(self.full, x_local)
         return self
 
+    def gather_async(self, x_local):
+        """Start the exchange and return at once; ``wait()`` before the first op that reads it.  The
+        collective starts after the work already enqueued on the current stream and runs beside
+        what is enqueued afterwards, so a caller whose next feature matrix is already available can
+        exchange it while the current ops compute (NCCL backend; otherwise this is ``gather``)."""
+        self._work = None
+        if self.world == 1 or dist.get_backend(self.group) != "nccl":
+            return self.gather(x_local)
+        rows = self.row_hi - self.row_lo
+        mine = self.full[self.rank * self.slot:(self.rank + 1) * self.slot]
+        mine[:rows].copy_(x_local)
+        try:
+            self._work = dist.all_gather_into_tensor(self.full, mine, group=self.group, async_op=True)
+        except Exception as exc:
+            raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (self.rank, self.world, exc)) from exc
+        return self
+
+    def wait(self):
+        """Make the current stream wait for the exchange started by ``gather_async``."""
+        work = getattr(self, "_work", None)
+        if work is not None:
+            try:
+                work.wait()
+            except Exception as exc:
+                raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (self.rank, self.world, exc)) from exc
+            self._work = None
+        return self
+
 
 class ShardedSpMM(_ShardedBase):
     """Row-sharded SpMM for a square adjacency.

@@ -48,6 +48,10 @@ def main():
         g = GatheredFeatures(bounds, d, device=device).gather(xl)
         np.testing.assert_array_equal(spmm.run(g).cpu().numpy(), want)
         np.testing.assert_array_equal(sddmm.run(g, yl).cpu().numpy(), e)
+        # the same exchange started early and waited for before use
+        g2 = GatheredFeatures(bounds, d, device=device)
+        g2.gather_async(xl)
+        np.testing.assert_array_equal(spmm.run(g2.wait()).cpu().numpy(), want)
         want_e = oracle.sddmm(coo.row, coo.col, x, y)[adj.indptr[lo]:adj.indptr[hi]]
         np.testing.assert_allclose(e, want_e, rtol=1e-5, atol=1e-4)
     dist.barrier()
