@@ -12,9 +12,9 @@
 // gathered from, and the tile width is chosen so that this slice stays resident in L2;
 // the CSR arrays are then the only DRAM stream.  The G lanes of a group read G*16
 // contiguous bytes per nonzero (one or more full 128-byte lines for G >= 8).  Column
-// indices and values are fetched G at a time, coalesced, one batch ahead of use, and
-// handed round the group with shuffles; the gathers of up to 8 nonzeros are issued
-// before the first of them is consumed.
+// indices (and values, unless the adjacency is unweighted) are fetched G at a time,
+// coalesced, one batch ahead of use, and passed to the group's lanes with shuffles; the
+// gathers of up to 8 nonzeros are issued before the first of them is consumed.
 //
 // Balance.  Rows are visited in the order of an fg_row_schedule (heaviest first), blocks
 // are launched in that order, and the groups sharing a warp hold neighbouring (hence

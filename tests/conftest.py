@@ -40,7 +40,8 @@ def oracle():
 def reference_util_or_skip():
     """The reference's own partitioners, loaded by file path, or skip where the checkout is absent."""
     import importlib.util
-    path = "/root/reference/python/featgraph/util/adj_partitioning.py"
+    root = os.environ.get("FEATGRAPH_REFERENCE_ROOT", os.path.join(os.path.expanduser("~"), "reference"))
+    path = os.path.join(root, "python", "featgraph", "util", "adj_partitioning.py")
     if not os.path.exists(path):
         pytest.skip("reference checkout not present on this machine")
     spec = importlib.util.spec_from_file_location("reference_adj_partitioning", path)

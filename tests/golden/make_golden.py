@@ -2,7 +2,7 @@
 
     python tests/golden/make_golden.py [path-to-reference-checkout]
 
-Needs the reference checkout (default /root/reference) only for the partition cases: its
+Needs the reference checkout (default: ``reference`` under the home directory) only for the partition cases: its
 ``python/featgraph/util/adj_partitioning.py`` is loaded by file path (it depends on numpy and
 scipy alone) and run on seeded random matrices.  The SpMM / SDDMM cases store what the
 reference's own tests compare against - ``adj.dot(X)`` (tests/test_module_spmm.py:29) and
@@ -71,7 +71,7 @@ def numeric_cases():
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.expanduser("~"), "reference")
     ref = load_reference_util(ref_root)
     np.savez_compressed(os.path.join(HERE, "partition_cases.npz"), **partition_cases(ref))
     np.savez_compressed(os.path.join(HERE, "numeric_cases.npz"), **numeric_cases())

@@ -40,7 +40,7 @@ if __name__ == "__main__":
     import tvm
     from tvm import te
 
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.expanduser("~"), "reference")
     path = os.path.join(ref_root, "python", "featgraph", "op", "vanilla_sddmm.py")
     spec = importlib.util.spec_from_file_location("reference_vanilla_sddmm", path)
     ref = importlib.util.module_from_spec(spec)

@@ -61,7 +61,7 @@ if __name__ == "__main__":
     import tvm
     from tvm import te, tir
 
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.expanduser("~"), "reference")
     ref_op = _load(ref_root, "python/featgraph/op/vanilla_spmm.py", "reference_vanilla_spmm")
     ref_util = _load(ref_root, "python/featgraph/util/adj_partitioning.py", "reference_adj_partitioning")
 
