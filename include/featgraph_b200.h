@@ -12,18 +12,22 @@
  * Conventions
  *  - Every pointer named d_* is a DEVICE pointer on the current CUDA device; h_* is a host
  *    pointer.  int32 index arrays and fp32 values, as the reference keeps scipy's dtypes
- *    (module/spmm.py:59-64).  Feature matrices are dense row-major, row stride = d.
- *  - The caller owns every array.  The library owns only the objects it hands out
- *    (fg_row_schedule, fg_graph) and frees them in the matching *_destroy call.
+ *    (module/spmm.py:59-64).  Feature matrices are dense row-major; the row stride is d unless a
+ *    stride argument says otherwise.
+ *  - The caller owns every array.  The library owns only the fg_row_schedule objects it hands
+ *    out (freed by fg_row_schedule_destroy), a pair of copy streams and a pool of events per host
+ *    thread that uses the host-buffer calls, and one static scratch array (fg_spmm_csr_f32_static).
  *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Device
  *    entry points only enqueue work on it; they do not synchronise.
  *  - Return value: FG_OK or an FG_ERR_* code; fg_last_error() gives the text for the
  *    calling thread.  Nothing aborts or traps.  Arguments are checked on the host only:
  *    index arrays are trusted to be in range (fg_csr_validate / fg_coo_validate check them).
- *  - Arithmetic: fp32, product and sum rounded separately (no fused multiply-add), the model
- *    of the reference's x86 target (module/spmm.py:202).  SpMM adds a row's nonzeros
- *    strictly in storage order, so its result does not depend on any launch parameter.
- *  - Re-entrant; no global mutable state except the thread-local error text.
+ *  - Arithmetic: fp32.  SpMM (all entry points) and fg_sddmm_coo_f32_exact round product and
+ *    sum separately (no fused multiply-add) and add in storage / ascending-k order: the values of
+ *    the reference's x86 loops, bit for bit, whatever the launch parameters.  fg_sddmm_coo_f32
+ *    sums each dot product as a fixed tree of FMAs (within fp32 rounding of d terms of that).
+ *  - Re-entrant; the mutable global state is the thread-local error text, the per-thread copy
+ *    streams, a launch counter and the static scratch array of fg_spmm_csr_f32_static.
  */
 #ifndef FEATGRAPH_B200_H_
 #define FEATGRAPH_B200_H_
