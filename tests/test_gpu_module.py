@@ -233,3 +233,22 @@ def test_sharded_wrappers_single_process(oracle):
     e = sd.run(torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()).cpu().numpy()
     coo = adj.tocoo()
     np.testing.assert_allclose(e, oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)
+
+
+def test_benchmark_scripts_read_npz_datasets(tmp_path):
+    """The reference's benchmarks take --dataset <scipy .npz> (CSR for SpMM, COO for SDDMM, as
+    benchmark/download_reddit_dataset.py:13,17 writes them); the counterparts here read the same files."""
+    import subprocess
+    import sys
+    from conftest import ROOT
+    adj = sp.random(300, 300, density=0.05, format="csr", random_state=7).astype("float32")
+    csr_path, coo_path = str(tmp_path / "g_csr.npz"), str(tmp_path / "g_coo.npz")
+    sp.save_npz(csr_path, adj)
+    sp.save_npz(coo_path, adj.tocoo())
+    for mod, path, target in (("bench_vanilla_spmm", csr_path, "cuda"), ("bench_vanilla_spmm", csr_path, "x86"),
+                              ("bench_vanilla_sddmm", coo_path, "cuda")):
+        r = subprocess.run([sys.executable, "-m", "featgraph_b200.benchmark." + mod, "--dataset", path,
+                            "--feat-len", "32", "--target", target], capture_output=True, text=True, cwd=ROOT,
+                           timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert "average time of 5 runs" in r.stdout
