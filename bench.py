@@ -417,14 +417,36 @@ def run_ours(args):
                         e2e_mod[("spmm", d)].run_host([xh], out=outs_host[d][0], wait=False)
                         e2e_mod[("sddmm", d)].run_host([xh, yh], out=outs_host[d][1], wait=False)
                     continue
-                xd = xh.to(device, non_blocking=True)
-                outs_host[d][0].copy_(spmm.run(xd), non_blocking=True)
-                sd = xh.to(device, non_blocking=True)
-                dd = yh.to(device, non_blocking=True)
-                outs_host[d][1].copy_(sddmm.run(sd, dd), non_blocking=True)
+                # N > 1: the same three stages with torch streams around the sharded calls (the
+                # exchange sits between copy-in and kernel): copies in on s_in, results out on s_out
+                xe, se, ye = stage_in[d]
+                with torch.cuda.stream(s_in):
+                    xe.copy_(xh, non_blocking=True)
+                    ev_x = s_in.record_event()
+                    se.copy_(xh, non_blocking=True)
+                    ye.copy_(yh, non_blocking=True)
+                    ev_sy = s_in.record_event()
+                stream.wait_event(ev_x)
+                o1 = spmm.run(xe)
+                ev_k1 = stream.record_event()
+                stream.wait_event(ev_sy)
+                o2 = sddmm.run(ye, o1) if WORKLOAD == "C4" else sddmm.run(se, ye)
+                ev_k2 = stream.record_event()
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_k1)
+                    outs_host[d][0].copy_(o1, non_blocking=True)
+                    s_out.wait_event(ev_k2)
+                    outs_host[d][1].copy_(o2, non_blocking=True)
             if world == 1:
                 featgraph_b200.host_sync(device)
+            else:
+                s_out.synchronize()
             stream.synchronize()
+
+        if world > 1:
+            s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+            stage_in = {d: tuple(torch.empty((hi - lo, d), dtype=torch.float32, device=device) for _ in range(3))
+                        for d in dims}
 
         # deferred calls must not share staging buffers: one module per (op, d) for the e2e leg
         e2e_mod = {}
