@@ -327,30 +327,39 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
 // of a single row (8 gathers per L2 round trip), so a 20,000-nonzero row alone takes 1.5 ms;
 // spmm_long_rows_kernel streams at about 13 TB/s (every slice crosses shared memory twice) but
 // needs only about 15 ns per nonzero of a row.  Units run tile-major, so a kernel's longest rows
-// are met again in its last feature tile: its time is modelled as
+// are met again in its last feature tile: alone, a kernel takes
 //     (1 - 1/tiles) * bytes / rate  +  max(bytes / rate / tiles, longest row's time).
-// The launch time for each candidate threshold is the long part plus the short part, and the
-// cheapest threshold wins.  A threshold fixed at schedule creation overrides the choice.  The
-// choice never affects a result bit.
+// Run one after the other, the launch takes the long part plus the short part.  Run side by side
+// (see spmm_dispatch) they share the path from L2, and the launch is modelled as the largest of:
+// both streams' bytes one after the other, and each kernel's own time with its streaming part
+// stretched to that sum.  The cheapest threshold wins.  A threshold fixed at schedule creation
+// overrides the choice.  The choice never affects a result bit.
 constexpr double kRowsRate = 17e12, kRowsSecPerNnz = 75e-9;
 constexpr double kRingRate = 13e12, kRingSecPerNnz = 15e-9;
 
-int64_t choose_long_rows(const fg_row_schedule& sch, int d, int short_tile) {
+int64_t choose_long_rows(const fg_row_schedule& sch, int d, int short_tile, bool side_by_side) {
     if (sch.fixed_threshold > 0) return sch.fixed_rows;
     const double short_tiles = (d + short_tile - 1) / short_tile;
     const double long_tiles = (d + 31) / 32;
     const double longest = (double)sch.max_row_nnz;
-    auto part = [](double bytes, double rate, double tiles, double row_time) {
-        const double stream = bytes / rate;
+    auto part = [](double stream, double tiles, double row_time) {
         return stream * (1.0 - 1.0 / tiles) + fmax(stream / tiles, row_time);
     };
     auto estimate = [&](double nnz_long, double threshold) {
+        const double stream_long = nnz_long * (4.0 * d + 8.0 * long_tiles) / kRingRate;
+        const double stream_short = (sch.nnz - nnz_long) * (4.0 * d + 8.0 * short_tiles) / kRowsRate;
+        const double long_row = longest * kRingSecPerNnz;
+        const double short_row = fmin(threshold, longest) * kRowsSecPerNnz;
         double t = 0.0;
-        if (nnz_long > 0)
-            t += part(nnz_long * (4.0 * d + 8.0 * long_tiles), kRingRate, long_tiles, longest * kRingSecPerNnz);
-        if (sch.nnz - nnz_long > 0)
-            t += part((sch.nnz - nnz_long) * (4.0 * d + 8.0 * short_tiles), kRowsRate, short_tiles,
-                      fmin(threshold, longest) * kRowsSecPerNnz);
+        if (side_by_side) {
+            const double both = stream_long + stream_short;
+            t = both;
+            if (nnz_long > 0) t = fmax(t, part(both, long_tiles, long_row));
+            if (sch.nnz - nnz_long > 0) t = fmax(t, part(both, short_tiles, short_row));
+        } else {
+            if (nnz_long > 0) t += part(stream_long, long_tiles, long_row);
+            if (sch.nnz - nnz_long > 0) t += part(stream_short, short_tiles, short_row);
+        }
         return t;
     };
     double best = estimate(0.0, longest);
@@ -364,6 +373,42 @@ int64_t choose_long_rows(const fg_row_schedule& sch, int d, int short_tile) {
         }
     }
     return best_rows;
+}
+
+// A second stream (per host thread and device) on which the long-row kernel can run beside
+// spmm_rows_kernel.  Fork and join are event waits on the device: the caller's stream sees one
+// call that is complete when both kernels are, also under stream capture.
+struct SideStream {
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    bool prepare() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return false;
+        if (dev != device) {  // a thread that moves to another device gets fresh objects there
+            stream = nullptr;
+            fork = join = nullptr;
+            device = dev;
+        }
+        if (!stream) {
+            int least = 0, greatest = 0;
+            cudaDeviceGetStreamPriorityRange(&least, &greatest);
+            // highest priority: the heaviest rows bound the launch, their blocks go first
+            if (cudaStreamCreateWithPriority(&stream, cudaStreamNonBlocking, greatest) != cudaSuccess ||
+                cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&join, cudaEventDisableTiming) != cudaSuccess) {
+                (void)cudaGetLastError();
+                stream = nullptr;
+                return false;
+            }
+        }
+        return true;
+    }
+};
+
+SideStream& side_stream() {
+    static thread_local SideStream s;
+    return s;
 }
 
 int launch_long(const SpmmArgs& a, cudaStream_t s) {
@@ -407,12 +452,8 @@ int launch(const SpmmArgs& a, bool dds, cudaStream_t s) {
     return FG_OK;
 }
 
-// Feature-tile width (floats) when the caller leaves the choice to the library: the widest
-// power of two, at most 128, whose gathered slice of x (n_cols rows of tile*4 bytes) fits the
-// share of L2 that stays resident under all-SM random access; never below 32 floats, one full
-// 128-byte line per gather.  If not even a 32-float slice fits, residency is out of reach and
-// the widest tile wins (fewest passes over the index arrays, longest contiguous gathers).
-int auto_tile(int64_t n_cols, int d) {
+// The share of L2 in which a gathered slice of x stays resident under all-SM random access.
+int64_t l2_budget() {
     static thread_local int64_t l2_bytes = -1;
     if (l2_bytes < 0) {
         int dev = 0, v = 0;
@@ -422,9 +463,21 @@ int auto_tile(int64_t n_cols, int d) {
         else
             l2_bytes = 64ll << 20;
     }
-    const int64_t budget = l2_bytes / 2;  // each half of the chip caches its own copy
+    return l2_bytes / 2;  // each half of the chip caches its own copy
+}
+
+// Can a 32-float slice of x (the narrowest tile that gathers whole 128-byte lines) stay in L2?
+bool slice_can_stay_in_l2(int64_t n_cols) { return n_cols * 32 * 4 <= l2_budget(); }
+
+// Feature-tile width (floats) when the caller leaves the choice to the library: the widest
+// power of two, at most 128, whose gathered slice of x (n_cols rows of tile*4 bytes) fits the
+// share of L2 that stays resident under all-SM random access; never below 32 floats, one full
+// 128-byte line per gather.  If not even a 32-float slice fits, residency is out of reach and
+// the widest tile wins (fewest passes over the index arrays, longest contiguous gathers).
+int auto_tile(int64_t n_cols, int d) {
+    const int64_t budget = l2_budget();
     const int cap = fg::pow2_ceil(d < 128 ? d : 128);
-    if (n_cols * 32 * 4 > budget) return cap;
+    if (!slice_can_stay_in_l2(n_cols)) return cap;
     int tile = 32;
     while (tile * 2 <= cap && n_cols * (int64_t)(tile * 2) * 4 <= budget) tile *= 2;
     return tile < cap ? tile : cap;
@@ -484,26 +537,49 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     if (tile > cap) tile = cap;
     if (tile < 4) tile = 4;
     // Long rows first, through the shared-memory ring (CSR with a schedule only).
-    const int64_t n_long = (schedule && !dds) ? choose_long_rows(*schedule, d, tile) : 0;
+    //
+    // When no slice of x can stay in L2 (graphs of millions of columns) the long-row kernel runs on
+    // a side stream, beside spmm_rows_kernel: its last rows - a few warps, each bound by its row's
+    // length (a 160,000-nonzero hub row takes 2.4 ms) - then finish under the other kernel instead
+    // of idling the GPU (R-MAT scale 22, d = 128: 7.5 -> 5.7 ms).  When a slice can stay resident
+    // the kernels run one after the other: side by side each would evict the slice the other one
+    // lives on (measured on the 233K-node graph: up to 25 % slower than in sequence).
+    const bool side_by_side = !slice_can_stay_in_l2(n_cols);
+    const int64_t n_long = (schedule && !dds) ? choose_long_rows(*schedule, d, tile, side_by_side) : 0;
+    bool forked = false;
+    SideStream& side = side_stream();
     if (n_long > 0) {
         SpmmArgs h = a;
         h.n_sched = (int32_t)n_long;
         h.n_tiles = (d + 31) / 32;
-        const int rc = launch_long(h, s);
-        if (rc != FG_OK) return rc;
         a.order_begin = (int32_t)n_long;
         a.n_sched = (int32_t)(n_rows - n_long);
-        if (a.n_sched == 0) return FG_OK;
+        // the two kernels write disjoint rows
+        forked = side_by_side && a.n_sched > 0 && side.prepare() &&
+                 cudaEventRecord(side.fork, s) == cudaSuccess &&
+                 cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
+        const int rc = launch_long(h, forked ? side.stream : s);
+        // record the join point even after a failed launch: the side stream must come back to the
+        // caller's stream (a capture could not end otherwise)
+        if (forked) FG_CUDA_TRY(cudaEventRecord(side.join, side.stream));
+        if (rc != FG_OK || a.n_sched == 0) {
+            if (forked) FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join, 0));
+            return rc;
+        }
     }
     a.n_tiles = (d + tile - 1) / tile;
+    int rc;
     switch (tile / 4) {
-        case 1: return launch<1, 4>(a, dds, s);
-        case 2: return launch<2, 4>(a, dds, s);
-        case 4: return launch<4, 4>(a, dds, s);
-        case 8: return launch<8, 4>(a, dds, s);
-        case 16: return launch<16, 4>(a, dds, s);
-        default: return launch<32, 4>(a, dds, s);
+        case 1: rc = launch<1, 4>(a, dds, s); break;
+        case 2: rc = launch<2, 4>(a, dds, s); break;
+        case 4: rc = launch<4, 4>(a, dds, s); break;
+        case 8: rc = launch<8, 4>(a, dds, s); break;
+        case 16: rc = launch<16, 4>(a, dds, s); break;
+        default: rc = launch<32, 4>(a, dds, s); break;
     }
+    // join: work enqueued on the caller's stream after this call waits for the long rows too
+    if (forked) FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join, 0));
+    return rc;
 }
 
 }  // namespace
