@@ -104,6 +104,10 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
         if (long_row_threshold > 0 && k >= long_row_threshold) {
             sch->fixed_rows = i + 1;
             sch->fixed_nnz = running + k;
+            if (k >= fg::kFixedHeavyFactor * long_row_threshold) {
+                sch->fixed_heavy_rows = i + 1;
+                sch->fixed_heavy_nnz = running + k;
+            }
         }
         running += k;
     }

@@ -5,6 +5,7 @@
 namespace fg {
 constexpr int kSplitLevels = 16;  // candidate long-row thresholds 64, 128, ..., 2^21
 inline int64_t split_threshold(int level) { return (int64_t)64 << level; }
+constexpr int64_t kFixedHeavyFactor = 16;
 }  // namespace fg
 
 struct fg_row_schedule {
@@ -16,8 +17,11 @@ struct fg_row_schedule {
     // candidate threshold: how many rows that is and how many nonzeros they hold.
     int64_t rows_at_least[fg::kSplitLevels] = {0};
     int64_t nnz_at_least[fg::kSplitLevels] = {0};
-    // A caller-fixed threshold (0 = let each launch choose among the candidates).
+    // A caller-fixed threshold (0 = let each launch choose among the candidates): rows with at least
+    // fixed_threshold nonzeros are long, those with at least kFixedHeavyFactor times as many are heavy.
     int64_t fixed_threshold = 0;
     int64_t fixed_rows = 0;
     int64_t fixed_nnz = 0;
+    int64_t fixed_heavy_rows = 0;
+    int64_t fixed_heavy_nnz = 0;
 };

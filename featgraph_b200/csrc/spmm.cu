@@ -22,10 +22,12 @@
 //
 // Long rows.  A row cannot be split between workers (its sum is sequential), so the time of
 // the longest row is a floor under the whole launch: with 8 gathers in flight a 20,000-nonzero
-// row costs 2,500 dependent round trips to L2.  Rows the schedule marks as long therefore go
-// to spmm_long_rows_kernel, which stages feature slices through a shared-memory ring filled by
-// cp.async (64 nonzeros in flight per row; the same sums, a deeper pipeline), and is launched
-// first; the remaining rows follow in spmm_rows_kernel.
+// row costs 2,500 dependent round trips to L2.  Rows the launch counts as long therefore go to
+// spmm_long_rows_kernel, which stages feature slices through a shared-memory ring filled by
+// cp.async (64 nonzeros in flight per row; the same sums, a deeper pipeline, 15 ns per nonzero of
+// a row instead of 75), and the very longest to spmm_heavy_rows_kernel, where the warps of a block
+// share one row's ring and take turns at its sum (7 ns per nonzero).  They are launched first; the
+// remaining rows follow in spmm_rows_kernel.
 #include <cmath>
 #include <mutex>
 
@@ -216,6 +218,44 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// A shared-memory load the compiler may not move: the consumers below issue a batch of these before
+// the first add of their (strictly sequential) chain, which keeps the load latency off that chain.
+__device__ __forceinline__ float lds_pinned(unsigned addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds4_pinned(unsigned addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+// adds (UNIT) or multiply-adds the kRingNnz slices of a full slot to acc, in order
+template <bool UNIT>
+__device__ __forceinline__ float drain_full_slot(float acc, const float* slot, int lane) {
+    constexpr int kBatch = 16;
+    const unsigned base = (unsigned)__cvta_generic_to_shared(slot);
+#pragma unroll
+    for (int h = 0; h < kRingNnz; h += kBatch) {
+        float t[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) t[j] = lds_pinned(base + ((h + j) * 32 + lane) * 4);
+        if (!UNIT) {
+#pragma unroll
+            for (int j4 = 0; j4 < kBatch; j4 += 4) {
+                const float4 v = lds4_pinned(base + (kRingNnz * 32 + h + j4) * 4);
+                t[j4 + 0] = __fmul_rn(v.x, t[j4 + 0]);
+                t[j4 + 1] = __fmul_rn(v.y, t[j4 + 1]);
+                t[j4 + 2] = __fmul_rn(v.z, t[j4 + 2]);
+                t[j4 + 3] = __fmul_rn(v.w, t[j4 + 3]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) acc = __fadd_rn(acc, t[j]);
+    }
+    return acc;
+}
+
 template <bool UNIT>
 __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const SpmmArgs a) {
     extern __shared__ __align__(16) float ring_smem[];
@@ -294,22 +334,10 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
             __syncwarp();                // ... and so have the other lanes'
             const float* slot = ring + (s % kRingStages) * kSlotFloats;
             const int cnt = min(kRingNnz, len - s * kRingNnz);
-            if (UNIT) {
-                if (cnt == kRingNnz) {
-#pragma unroll
-                    for (int j = 0; j < kRingNnz; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
-                } else {
-                    for (int j = 0; j < cnt; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
-                }
-            } else if (cnt == kRingNnz) {
-#pragma unroll
-                for (int j4 = 0; j4 < kRingNnz; j4 += 4) {
-                    const float4 v = *reinterpret_cast<const float4*>(slot + kRingNnz * 32 + j4);
-                    acc = fg::mul_then_add(acc, v.x, slot[(j4 + 0) * 32 + lane]);
-                    acc = fg::mul_then_add(acc, v.y, slot[(j4 + 1) * 32 + lane]);
-                    acc = fg::mul_then_add(acc, v.z, slot[(j4 + 2) * 32 + lane]);
-                    acc = fg::mul_then_add(acc, v.w, slot[(j4 + 3) * 32 + lane]);
-                }
+            if (cnt == kRingNnz) {
+                acc = drain_full_slot<UNIT>(acc, slot, lane);
+            } else if (UNIT) {
+                for (int j = 0; j < cnt; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
             } else {
                 for (int j = 0; j < cnt; ++j)
                     acc = fg::mul_then_add(acc, slot[kRingNnz * 32 + j], slot[j * 32 + lane]);
@@ -320,59 +348,205 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
     if (col0 + lane < a.d) a.out[(int64_t)row * a.ldo + col0 + lane] = acc;
 }
 
-// How many rows (from the front of the schedule) go to the long-row kernel for this launch.
+// ---------------------------------------------------------------------------------------------
+// Heaviest rows: one BLOCK per (row, 32-float tile) unit.
 //
-// The two kernels trade throughput against the time of one long row.  Measured on B200 (C2
-// graph): spmm_rows_kernel streams gathers at about 17 TB/s but spends about 75 ns per nonzero
-// of a single row (8 gathers per L2 round trip), so a 20,000-nonzero row alone takes 1.5 ms;
-// spmm_long_rows_kernel streams at about 13 TB/s (every slice crosses shared memory twice) but
-// needs only about 15 ns per nonzero of a row.  Units run tile-major, so a kernel's longest rows
-// are met again in its last feature tile: alone, a kernel takes
+// A single warp cannot keep more than a few stages of cp.async copies in flight (a deeper ring per
+// warp did not raise its rate: 11 ns per nonzero with 11 stages in flight against 13-15 ns with 2),
+// so the time of one row in spmm_long_rows_kernel is about 15 ns per nonzero whatever the ring's
+// depth.  Here the W warps of a block share one row: stage g (32 nonzeros) belongs to warp g % W,
+// which copies it into its own 3-slot ring exactly as above, so 3 W stages are in flight per row.
+// The sum stays one sequential chain: the warps take turns in stage order, the running sums (lane f
+// = output column f) pass from warp to warp through shared memory, one block barrier per stage.
+// The warp whose turn comes next waits for its copies while the current one adds.
+// ---------------------------------------------------------------------------------------------
+template <int W>
+constexpr int heavy_smem_bytes() {
+    return (W * kRingStages * kSlotFloats + 32) * 4;
+}
+
+template <bool UNIT, int W>
+__global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs a) {
+    static_assert(W >= 2 && (W & (W - 1)) == 0, "W: a power of two, at least 2");
+    extern __shared__ __align__(16) float ring_smem[];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    float* ring = ring_smem + warp * (kRingStages * kSlotFloats);
+    float* sums = ring_smem + W * kRingStages * kSlotFloats;  // the 32 running sums between turns
+
+    const int tile = (int)(blockIdx.x / (unsigned)a.n_sched);
+    const int row = a.order[a.order_begin + (int)(blockIdx.x - (unsigned)tile * (unsigned)a.n_sched)];
+    const int col0 = tile * 32;
+    const int start = a.pos[row];
+    const int len = a.pos[row + 1] - start;
+    const int n_stages = (len + kRingNnz - 1) / kRingNnz;  // the same for every warp of the block
+    // this warp's stages: local stage i is stage i * W + warp of the row
+    const int my_stages = n_stages > warp ? (n_stages - warp + W - 1) / W : 0;
+
+    const int piece = lane & 7;
+    const int sub = lane >> 3;
+    const bool piece_ok = col0 + piece * 4 < a.d;
+    const float* xpiece = a.x + col0 + piece * 4;
+    const int ldx32 = (int)a.ldx;
+
+    auto fetch_ids = [&](int i, int& c, float& v) {  // nonzero `lane` of local stage i
+        const int k = (i * W + warp) * kRingNnz + lane;
+        c = -1;
+        v = 0.f;
+        if (i < my_stages && k < len) {
+            c = a.idx[start + k];
+            if (!UNIT) v = a.vals[start + k];
+        }
+    };
+    auto fill = [&](int i, int c_mine, float v_mine) {
+        float* slot = ring + (i % kRingStages) * kSlotFloats;
+        if (i < my_stages) {
+            if (!UNIT) slot[kRingNnz * 32 + lane] = v_mine;
+#pragma unroll
+            for (int j = 0; j < kRingNnz / 4; ++j) {
+                const int nz = j * 4 + sub;
+                const int c = __shfl_sync(0xffffffffu, c_mine, nz);
+                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * ldx32);
+            }
+        }
+        cp_async_commit();  // one group per local stage, empty past the end
+    };
+
+    // all three slots are filled up front; ids for the two local stages after them wait in registers
+    int c_next, c_after;
+    float v_next, v_after;
+    {
+        int c0[kRingStages];
+        float v0[kRingStages];
+#pragma unroll
+        for (int i = 0; i < kRingStages; ++i) fetch_ids(i, c0[i], v0[i]);
+        fetch_ids(kRingStages, c_next, v_next);
+        fetch_ids(kRingStages + 1, c_after, v_after);
+#pragma unroll
+        for (int i = 0; i < kRingStages; ++i) fill(i, c0[i], v0[i]);
+    }
+    if (n_stages == 0) {
+        if (warp == 0 && col0 + lane < a.d) a.out[(int64_t)row * a.ldo + col0 + lane] = 0.f;
+        return;
+    }
+    // Turn s is passed from its owner to the owner of s + 1 through a named barrier shared by just
+    // those two warps (barrier 1 + w: warp w arrives, warp w + 1 waits), so a warp that has had its
+    // turn refills its slot while the following turns proceed.  Each stage after the first has one
+    // arrival (by the previous stage's owner) and one wait (by its owner): the counts always match.
+    const int bar_mine = 1 + warp;
+    const int bar_prev = 1 + ((warp + W - 1) & (W - 1));
+#pragma unroll 1
+    for (int i = 0; i < my_stages; ++i) {
+        const int s = i * W + warp;
+        cp_async_wait<kRingStages - 1>();  // my copies of local stage i (all but the two newest groups)
+        __syncwarp();
+        float acc = 0.f;
+        if (s > 0) {
+            asm volatile("bar.sync %0, 64;\n" ::"r"(bar_prev) : "memory");
+            acc = sums[lane];
+        }
+        const float* slot = ring + (i % kRingStages) * kSlotFloats;
+        const int cnt = min(kRingNnz, len - s * kRingNnz);
+        if (cnt == kRingNnz) {
+            acc = drain_full_slot<UNIT>(acc, slot, lane);
+        } else if (UNIT) {
+            for (int j = 0; j < cnt; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
+        } else {
+            for (int j = 0; j < cnt; ++j)
+                acc = fg::mul_then_add(acc, slot[kRingNnz * 32 + j], slot[j * 32 + lane]);
+        }
+        if (s + 1 < n_stages) {
+            sums[lane] = acc;
+            __threadfence_block();
+            asm volatile("bar.arrive %0, 64;\n" ::"r"(bar_mine) : "memory");
+        } else if (col0 + lane < a.d) {
+            a.out[(int64_t)row * a.ldo + col0 + lane] = acc;  // the row's last stage
+        }
+        __syncwarp();  // every lane has read the slot
+        // refill the slot just drained, off the chain of turns
+        fill(i + kRingStages, c_next, v_next);
+        c_next = c_after;
+        v_next = v_after;
+        fetch_ids(i + kRingStages + 2, c_after, v_after);
+    }
+}
+
+// Which rows (from the front of the schedule) go to the heavy-row and long-row kernels for this launch.
+//
+// The three kernels trade throughput against the time of one row.  Measured on B200 (C2 graph):
+//   spmm_rows_kernel       streams gathers at about 17 TB/s, about 75 ns per nonzero of one row
+//                          (8 gathers per L2 round trip): a 20,000-nonzero row alone takes 1.5 ms;
+//   spmm_long_rows_kernel  about 13 TB/s (every slice crosses shared memory twice), 15 ns per nonzero;
+//   spmm_heavy_rows_kernel about 9 TB/s (a block's warps take turns), 7 ns per nonzero.
+// Units run tile-major, so a kernel's longest rows are met again in its last feature tile: alone, a
+// kernel takes
 //     (1 - 1/tiles) * bytes / rate  +  max(bytes / rate / tiles, longest row's time).
-// Run one after the other, the launch takes the long part plus the short part.  Run side by side
-// (see spmm_dispatch) they share the path from L2, and the launch is modelled as the largest of:
-// both streams' bytes one after the other, and each kernel's own time with its streaming part
-// stretched to that sum.  The cheapest threshold wins.  A threshold fixed at schedule creation
-// overrides the choice.  The choice never affects a result bit.
+// Run one after the other, the launch takes the sum of the parts.  Run side by side (heavy then long
+// rows on a second stream, see spmm_dispatch) the streams share the path from L2, and the launch is
+// modelled as the largest of: all bytes one after the other, and each stream's own time with its
+// streaming parts stretched to that sum.  Every pair of candidate thresholds is tried and the
+// cheapest wins.  A threshold fixed at schedule creation overrides the choice.  The choice never
+// affects a result bit.
 constexpr double kRowsRate = 17e12, kRowsSecPerNnz = 75e-9;
 constexpr double kRingRate = 13e12, kRingSecPerNnz = 15e-9;
+constexpr double kHeavyRate = 9e12, kHeavySecPerNnz = 7.5e-9;
 
-int64_t choose_long_rows(const fg_row_schedule& sch, int d, int short_tile, bool side_by_side) {
-    if (sch.fixed_threshold > 0) return sch.fixed_rows;
+struct RowSplit {
+    int64_t heavy = 0;  // order[0, heavy): spmm_heavy_rows_kernel
+    int64_t ring = 0;   // order[heavy, ring): spmm_long_rows_kernel; the rest: spmm_rows_kernel
+};
+
+RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, bool side_by_side) {
+    RowSplit best_split;
+    if (sch.fixed_threshold > 0) {
+        best_split.heavy = sch.fixed_heavy_rows;
+        best_split.ring = sch.fixed_rows;
+        return best_split;
+    }
     const double short_tiles = (d + short_tile - 1) / short_tile;
     const double long_tiles = (d + 31) / 32;
     const double longest = (double)sch.max_row_nnz;
+    const double long_bytes = 4.0 * d + 8.0 * long_tiles, short_bytes = 4.0 * d + 8.0 * short_tiles;
     auto part = [](double stream, double tiles, double row_time) {
-        return stream * (1.0 - 1.0 / tiles) + fmax(stream / tiles, row_time);
+        return stream <= 0.0 ? 0.0 : stream * (1.0 - 1.0 / tiles) + fmax(stream / tiles, row_time);
     };
-    auto estimate = [&](double nnz_long, double threshold) {
-        const double stream_long = nnz_long * (4.0 * d + 8.0 * long_tiles) / kRingRate;
-        const double stream_short = (sch.nnz - nnz_long) * (4.0 * d + 8.0 * short_tiles) / kRowsRate;
-        const double long_row = longest * kRingSecPerNnz;
-        const double short_row = fmin(threshold, longest) * kRowsSecPerNnz;
-        double t = 0.0;
-        if (side_by_side) {
-            const double both = stream_long + stream_short;
-            t = both;
-            if (nnz_long > 0) t = fmax(t, part(both, long_tiles, long_row));
-            if (sch.nnz - nnz_long > 0) t = fmax(t, part(both, short_tiles, short_row));
-        } else {
-            if (nnz_long > 0) t += part(stream_long, long_tiles, long_row);
-            if (sch.nnz - nnz_long > 0) t += part(stream_short, short_tiles, short_row);
-        }
-        return t;
+    // thresholds t_heavy >= t_ring; "none" is a threshold above the longest row
+    auto estimate = [&](double nnz_heavy, double t_heavy, double nnz_ring_up, double t_ring) {
+        const double nnz_ring = nnz_ring_up - nnz_heavy, nnz_rows = (double)sch.nnz - nnz_ring_up;
+        const double s_heavy = nnz_heavy * long_bytes / kHeavyRate;
+        const double s_ring = nnz_ring * long_bytes / kRingRate;
+        const double s_rows = nnz_rows * short_bytes / kRowsRate;
+        const double heavy_row = longest * kHeavySecPerNnz;
+        const double ring_row = fmin(t_heavy, longest) * kRingSecPerNnz;
+        const double rows_row = fmin(t_ring, longest) * kRowsSecPerNnz;
+        if (!side_by_side)
+            return part(s_heavy, long_tiles, heavy_row) + part(s_ring, long_tiles, ring_row) +
+                   part(s_rows, short_tiles, rows_row);
+        const double all = s_heavy + s_ring + s_rows;
+        const double stretch = s_heavy + s_ring > 0.0 ? all / (s_heavy + s_ring) : 1.0;
+        const double side = part(s_heavy * stretch, long_tiles, heavy_row) + part(s_ring * stretch, long_tiles, ring_row);
+        const double main = s_rows > 0.0 ? part(all, short_tiles, rows_row) : 0.0;
+        return fmax(all, fmax(side, main));
     };
-    double best = estimate(0.0, longest);
-    int64_t best_rows = 0;
-    for (int level = 0; level < fg::kSplitLevels; ++level) {
-        if (sch.rows_at_least[level] == 0) break;
-        const double t = estimate((double)sch.nnz_at_least[level], (double)fg::split_threshold(level));
-        if (t < best) {
-            best = t;
-            best_rows = sch.rows_at_least[level];
+    const double none = longest + 1.0;
+    double best = estimate(0.0, none, 0.0, none);
+    for (int lr = 0; lr < fg::kSplitLevels; ++lr) {  // ring threshold
+        if (sch.rows_at_least[lr] == 0) break;
+        const double t_ring = (double)fg::split_threshold(lr);
+        for (int lh = lr; lh <= fg::kSplitLevels; ++lh) {  // heavy threshold, kSplitLevels = none
+            const bool no_heavy = lh == fg::kSplitLevels || sch.rows_at_least[lh] == 0;
+            const double t = no_heavy ? estimate(0.0, none, (double)sch.nnz_at_least[lr], t_ring)
+                                      : estimate((double)sch.nnz_at_least[lh], (double)fg::split_threshold(lh),
+                                                 (double)sch.nnz_at_least[lr], t_ring);
+            if (t < best) {
+                best = t;
+                best_split.heavy = no_heavy ? 0 : sch.rows_at_least[lh];
+                best_split.ring = sch.rows_at_least[lr];
+            }
+            if (no_heavy) break;
         }
     }
-    return best_rows;
+    return best_split;
 }
 
 // A second stream (per host thread and device) on which the long-row kernel can run beside
@@ -429,6 +603,26 @@ int launch_long(const SpmmArgs& a, cudaStream_t s) {
     FG_CUDA_TRY(cudaGetLastError());
     fg::count_launches(1);
     return FG_OK;
+}
+
+template <bool UNIT, int W>
+int launch_heavy_w(const SpmmArgs& a, cudaStream_t s) {
+    const int64_t blocks = (int64_t)a.n_sched * a.n_tiles;
+    if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
+    if (blocks == 0) return FG_OK;
+    static_assert(heavy_smem_bytes<W>() <= 227 * 1024, "rings do not fit in shared memory");
+    FG_CUDA_TRY(cudaFuncSetAttribute(spmm_heavy_rows_kernel<UNIT, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     heavy_smem_bytes<W>()));
+    spmm_heavy_rows_kernel<UNIT, W><<<(unsigned)blocks, W * 32, heavy_smem_bytes<W>(), s>>>(a);
+    FG_CUDA_TRY(cudaGetLastError());
+    fg::count_launches(1);
+    return FG_OK;
+}
+
+constexpr int kHeavyWarps = 4;  // 8 warps: the same time per row, lower throughput (5.7 against 9 TB/s)
+
+int launch_heavy(const SpmmArgs& a, cudaStream_t s) {
+    return a.vals == nullptr ? launch_heavy_w<true, kHeavyWarps>(a, s) : launch_heavy_w<false, kHeavyWarps>(a, s);
 }
 
 template <int G, int VEC>
@@ -536,29 +730,37 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     const int cap = fg::pow2_ceil(d);
     if (tile > cap) tile = cap;
     if (tile < 4) tile = 4;
-    // Long rows first, through the shared-memory ring (CSR with a schedule only).
+    // Heavy and long rows first, through the shared-memory rings (CSR with a schedule only).
     //
-    // When no slice of x can stay in L2 (graphs of millions of columns) the long-row kernel runs on
-    // a side stream, beside spmm_rows_kernel: its last rows - a few warps, each bound by its row's
-    // length (a 160,000-nonzero hub row takes 2.4 ms) - then finish under the other kernel instead
-    // of idling the GPU (R-MAT scale 22, d = 128: 7.5 -> 5.7 ms).  When a slice can stay resident
+    // When no slice of x can stay in L2 (graphs of millions of columns) those kernels run on a side
+    // stream, beside spmm_rows_kernel: their last rows - a few warps, each bound by its row's
+    // length (a 160,000-nonzero hub row takes 2.4 ms in the long-row kernel) - then finish under the
+    // other kernel instead of idling the GPU (R-MAT scale 22, d = 128: 7.5 -> 5.7 ms).  When a slice can stay resident
     // the kernels run one after the other: side by side each would evict the slice the other one
     // lives on (measured on the 233K-node graph: up to 25 % slower than in sequence).
     const bool side_by_side = !slice_can_stay_in_l2(n_cols);
-    const int64_t n_long = (schedule && !dds) ? choose_long_rows(*schedule, d, tile, side_by_side) : 0;
+    RowSplit split;
+    if (schedule && !dds) split = choose_row_split(*schedule, d, tile, side_by_side);
     bool forked = false;
     SideStream& side = side_stream();
-    if (n_long > 0) {
-        SpmmArgs h = a;
-        h.n_sched = (int32_t)n_long;
-        h.n_tiles = (d + 31) / 32;
-        a.order_begin = (int32_t)n_long;
-        a.n_sched = (int32_t)(n_rows - n_long);
-        // the two kernels write disjoint rows
+    if (split.ring > 0) {
+        a.order_begin = (int32_t)split.ring;
+        a.n_sched = (int32_t)(n_rows - split.ring);
+        // the kernels write disjoint rows
         forked = side_by_side && a.n_sched > 0 && side.prepare() &&
                  cudaEventRecord(side.fork, s) == cudaSuccess &&
                  cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
-        const int rc = launch_long(h, forked ? side.stream : s);
+        cudaStream_t ls = forked ? side.stream : s;
+        SpmmArgs h = a;
+        h.n_tiles = (d + 31) / 32;
+        h.order_begin = 0;
+        h.n_sched = (int32_t)split.heavy;
+        int rc = launch_heavy(h, ls);
+        if (rc == FG_OK) {
+            h.order_begin = (int32_t)split.heavy;
+            h.n_sched = (int32_t)(split.ring - split.heavy);
+            rc = launch_long(h, ls);
+        }
         // record the join point even after a failed launch: the side stream must come back to the
         // caller's stream (a capture could not end otherwise)
         if (forked) FG_CUDA_TRY(cudaEventRecord(side.join, side.stream));

@@ -69,9 +69,9 @@ int fg_device_info(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor, int6
 typedef struct fg_row_schedule fg_row_schedule;
 
 /* d_indptr: n_rows+1 ascending positions.  long_row_threshold: 0 = each SpMM launch decides
- * which rows count as long (see fg_spmm_csr_f32); > 0 fixes it: rows with at least that many
- * nonzeros always take the long-row kernel (INT32_MAX = none ever do).  Synchronises `stream`
- * before returning. */
+ * which rows count as long and which as heavy (see fg_spmm_csr_f32); > 0 fixes it: rows with at
+ * least that many nonzeros always take the long-row kernel, rows with at least 16 times as many
+ * the heavy-row kernel (INT32_MAX = none ever do).  Synchronises `stream` before returning. */
 int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long_row_threshold,
                            void* stream, fg_row_schedule** out_schedule);
 /* Device pointer to the n_rows row ids in visiting order (valid until destroy). */
@@ -90,7 +90,13 @@ void fg_row_schedule_destroy(fg_row_schedule* schedule);
  *              dataset script stores it, benchmark/download_reddit_dataset.py:11): the value array is
  *              then neither read nor multiplied in (1.0 * x == x exactly, so the result bits are
  *              those of an all-ones value array).  Also accepted by the DDS and static entry points.
- *   schedule   NULL = visit rows in index order.
+ *   schedule   NULL = visit rows in index order, one kernel.  With a schedule, rows are visited
+ *              heaviest first and each launch may hand its longest rows to two further kernels
+ *              (long rows: one warp per row and 32-float tile, slices staged through a
+ *              shared-memory ring; heavy rows: one block per row and tile, its warps taking
+ *              turns).  When no 32-float slice of x can stay in L2 those kernels run on an
+ *              internal second stream beside the main one, forked from and joined to `stream`
+ *              by events (legal under stream capture).  No effect on the values.
  *   feat_tile  width in floats of the feature slice handled per pass over the rows
  *              (power of two, 4..128), 0 = choose from n_cols and the L2 size.  It is the
  *              reference's num_feat_partitions idea (op/vanilla_spmm.py:41-44) used to keep

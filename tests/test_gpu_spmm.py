@@ -140,6 +140,26 @@ def test_long_rows_take_the_deep_pipeline_and_stay_exact(oracle, d):
     np.testing.assert_array_equal(G.spmm_csr(a.indptr, a.indices, a.data, x, use_schedule=False), want)
 
 
+@pytest.mark.parametrize("d", [4, 32, 36, 100, 128])
+@pytest.mark.parametrize("unit", [False, True])
+def test_heavy_rows_take_the_block_per_row_kernel_and_stay_exact(oracle, d, unit):
+    """With a fixed threshold T, rows of 16 T nonzeros and more go to the kernel in which the warps of
+    a block take turns on one row: fewer stages than warps, exact multiples of the 32-nonzero stage,
+    one more and one less, a long row, and the ring kernel and the plain kernel beside it."""
+    import gpu_util as G
+    from featgraph_b200 import graphgen
+    deg = np.array([16, 17, 31, 32, 33, 63, 64, 65, 95, 96, 97, 127, 128, 129, 160, 1000, 4099, 0, 3, 15, 256, 20001],
+                   dtype=np.int64)
+    a = graphgen._csr_from_degrees(deg, 30000, seed=301)
+    if not unit:
+        a.data = (np.random.default_rng(302).random(a.nnz, dtype=np.float32) * 2 - 1).astype(np.float32)
+    x = graphgen.uniform_features((30000, d), seed=303 + d)
+    want = oracle.spmm_csr(a.indptr, a.indices, a.data, x)
+    for threshold in (1, 2, 8, 64):  # heavy from 16, 32, 128, 1024 nonzeros
+        got = G.spmm_csr(a.indptr, a.indices, None if unit else a.data, x, long_row_threshold=threshold)
+        np.testing.assert_array_equal(got, want, err_msg="threshold %d" % threshold)
+
+
 def test_every_row_long(oracle):
     import gpu_util as G
     from featgraph_b200 import graphgen
