@@ -35,8 +35,11 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
     if (n_rows < 0 || n_rows > INT32_MAX)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "n_rows=%lld out of range", (long long)n_rows);
     if (n_rows > 0 && !d_indptr) return fg::fail(FG_ERR_INVALID_ARGUMENT, "d_indptr is NULL");
-    if (long_row_threshold < 0)
-        return fg::fail(FG_ERR_INVALID_ARGUMENT, "long_row_threshold must be >= 0 (0 = default)");
+    if (long_row_threshold == INT32_MIN)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "long_row_threshold out of range");
+    // a negative threshold fixes |threshold| and asks for the 8-warp form of the heavy-row kernel
+    const bool fixed_wide = long_row_threshold < 0;
+    if (fixed_wide) long_row_threshold = -long_row_threshold;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     fg_row_schedule* sch = new fg_row_schedule();
     sch->n_rows = n_rows;
@@ -92,6 +95,7 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
     cleanup();
     sch->max_row_nnz = h_keys[0];
     sch->fixed_threshold = long_row_threshold;
+    sch->fixed_wide = fixed_wide;
     int level = fg::kSplitLevels - 1;
     int64_t running = 0;
     for (int64_t i = 0; i < n_rows; ++i) {  // descending counts: thresholds are crossed downwards

@@ -24,4 +24,5 @@ struct fg_row_schedule {
     int64_t fixed_nnz = 0;
     int64_t fixed_heavy_rows = 0;
     int64_t fixed_heavy_nnz = 0;
+    bool fixed_wide = false;  // heavy rows with 8 warps per block instead of 4
 };

@@ -351,28 +351,37 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
 // ---------------------------------------------------------------------------------------------
 // Heaviest rows: one BLOCK per (row, 32-float tile) unit.
 //
-// A single warp cannot keep more than a few stages of cp.async copies in flight (a deeper ring per
-// warp did not raise its rate: 11 ns per nonzero with 11 stages in flight against 13-15 ns with 2),
-// so the time of one row in spmm_long_rows_kernel is about 15 ns per nonzero whatever the ring's
-// depth.  Here the W warps of a block share one row: stage g (32 nonzeros) belongs to warp g % W,
-// which copies it into its own 3-slot ring exactly as above, so 3 W stages are in flight per row.
-// The sum stays one sequential chain: the warps take turns in stage order, the running sums (lane f
-// = output column f) pass from warp to warp through shared memory, one block barrier per stage.
-// The warp whose turn comes next waits for its copies while the current one adds.
+// In spmm_long_rows_kernel one warp does everything for its row - column ids, address arithmetic,
+// copies, waits and the adds - about 130 mostly dependent instructions per 32 nonzeros, and that
+// chain, not the ring's depth, sets the row's pace (15 ns per nonzero; a ring of 12 slots gave 11).
+// Here the W warps of a block share one row, and only the adds stay on the row's chain.  The row is
+// cut into turns of TURN stages (32 nonzeros each); turn t belongs to warp t % W, which copies its
+// stages into its own ring (3 turns deep) exactly as above.  The sum stays one sequential chain:
+// the warps take their turns in order and hand the 32 running sums (lane f = output column f) on
+// through shared memory and a named barrier shared by just the two warps involved (barrier 1 + w:
+// warp w arrives, warp w + 1 waits).  A warp whose turn is over refills its slots, fetches ids and
+// waits for its next copies while the other warps have their turns; before its turn it has
+// already loaded the first stage's 32 values into registers, so a turn costs the barrier, one
+// shared load of the sums and the chain of adds: about 3 to 4 ns per nonzero.
+// Each turn after the first has one arrival (by the previous turn's owner) and one wait (by its
+// owner) on the same barrier, so the counts always match; there is no spinning anywhere.
 // ---------------------------------------------------------------------------------------------
-template <int W>
+constexpr int kHeavyTurnsDeep = 3;  // turns of its own that a warp keeps in its ring
+
+template <int W, int TURN>
 constexpr int heavy_smem_bytes() {
-    return (W * kRingStages * kSlotFloats + 32) * 4;
+    return (W * kHeavyTurnsDeep * TURN * kSlotFloats + 32) * 4;
 }
 
-template <bool UNIT, int W>
+template <bool UNIT, int W, int TURN>
 __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs a) {
     static_assert(W >= 2 && (W & (W - 1)) == 0, "W: a power of two, at least 2");
+    constexpr int kSlots = kHeavyTurnsDeep * TURN;  // per warp
     extern __shared__ __align__(16) float ring_smem[];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    float* ring = ring_smem + warp * (kRingStages * kSlotFloats);
-    float* sums = ring_smem + W * kRingStages * kSlotFloats;  // the 32 running sums between turns
+    float* ring = ring_smem + warp * (kSlots * kSlotFloats);
+    float* sums = ring_smem + W * kSlots * kSlotFloats;  // the 32 running sums between turns
 
     const int tile = (int)(blockIdx.x / (unsigned)a.n_sched);
     const int row = a.order[a.order_begin + (int)(blockIdx.x - (unsigned)tile * (unsigned)a.n_sched)];
@@ -380,8 +389,15 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
     const int start = a.pos[row];
     const int len = a.pos[row + 1] - start;
     const int n_stages = (len + kRingNnz - 1) / kRingNnz;  // the same for every warp of the block
-    // this warp's stages: local stage i is stage i * W + warp of the row
-    const int my_stages = n_stages > warp ? (n_stages - warp + W - 1) / W : 0;
+    if (n_stages == 0) {
+        if (warp == 0 && col0 + lane < a.d) a.out[(int64_t)row * a.ldo + col0 + lane] = 0.f;
+        return;
+    }
+    const int n_turns = (n_stages + TURN - 1) / TURN;
+    const int my_turns = n_turns > warp ? (n_turns - warp + W - 1) / W : 0;
+    // this warp's local stage i = (its turn i / TURN, stage i % TURN of that turn) is stage
+    // ((i / TURN) * W + warp) * TURN + i % TURN of the row
+    auto row_stage = [&](int i) { return ((i / TURN) * W + warp) * TURN + i % TURN; };
 
     const int piece = lane & 7;
     const int sub = lane >> 3;
@@ -390,17 +406,17 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
     const int ldx32 = (int)a.ldx;
 
     auto fetch_ids = [&](int i, int& c, float& v) {  // nonzero `lane` of local stage i
-        const int k = (i * W + warp) * kRingNnz + lane;
+        const int k = row_stage(i) * kRingNnz + lane;
         c = -1;
         v = 0.f;
-        if (i < my_stages && k < len) {
+        if (k < len) {  // also false for every stage past the row's end
             c = a.idx[start + k];
             if (!UNIT) v = a.vals[start + k];
         }
     };
     auto fill = [&](int i, int c_mine, float v_mine) {
-        float* slot = ring + (i % kRingStages) * kSlotFloats;
-        if (i < my_stages) {
+        float* slot = ring + (i % kSlots) * kSlotFloats;
+        if (row_stage(i) < n_stages) {
             if (!UNIT) slot[kRingNnz * 32 + lane] = v_mine;
 #pragma unroll
             for (int j = 0; j < kRingNnz / 4; ++j) {
@@ -412,62 +428,95 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
         cp_async_commit();  // one group per local stage, empty past the end
     };
 
-    // all three slots are filled up front; ids for the two local stages after them wait in registers
-    int c_next, c_after;
-    float v_next, v_after;
+    // every slot is filled up front; the ids of the two turns after those wait in registers (they
+    // stream from DRAM and must be there when the refill needs them)
+    int c_next[TURN], c_after[TURN];
+    float v_next[TURN], v_after[TURN];
     {
-        int c0[kRingStages];
-        float v0[kRingStages];
+        int c0[kSlots];
+        float v0[kSlots];
 #pragma unroll
-        for (int i = 0; i < kRingStages; ++i) fetch_ids(i, c0[i], v0[i]);
-        fetch_ids(kRingStages, c_next, v_next);
-        fetch_ids(kRingStages + 1, c_after, v_after);
+        for (int i = 0; i < kSlots; ++i) fetch_ids(i, c0[i], v0[i]);
 #pragma unroll
-        for (int i = 0; i < kRingStages; ++i) fill(i, c0[i], v0[i]);
+        for (int u = 0; u < TURN; ++u) {
+            fetch_ids(kSlots + u, c_next[u], v_next[u]);
+            fetch_ids(kSlots + TURN + u, c_after[u], v_after[u]);
+        }
+#pragma unroll
+        for (int i = 0; i < kSlots; ++i) fill(i, c0[i], v0[i]);
     }
-    if (n_stages == 0) {
-        if (warp == 0 && col0 + lane < a.d) a.out[(int64_t)row * a.ldo + col0 + lane] = 0.f;
-        return;
-    }
-    // Turn s is passed from its owner to the owner of s + 1 through a named barrier shared by just
-    // those two warps (barrier 1 + w: warp w arrives, warp w + 1 waits), so a warp that has had its
-    // turn refills its slot while the following turns proceed.  Each stage after the first has one
-    // arrival (by the previous stage's owner) and one wait (by its owner): the counts always match.
+
     const int bar_mine = 1 + warp;
     const int bar_prev = 1 + ((warp + W - 1) & (W - 1));
 #pragma unroll 1
-    for (int i = 0; i < my_stages; ++i) {
-        const int s = i * W + warp;
-        cp_async_wait<kRingStages - 1>();  // my copies of local stage i (all but the two newest groups)
+    for (int t = 0; t < my_turns; ++t) {
+        const int i0 = t * TURN;        // first local stage of the turn
+        const int s0 = row_stage(i0);   // and its stage of the row
+        // my copies of this turn: all but the (kHeavyTurnsDeep - 1) * TURN newest groups
+        cp_async_wait<(kHeavyTurnsDeep - 1) * TURN>();
         __syncwarp();
+        // the first stage's values (products) go to registers before the turn starts
+        const float* slot0 = ring + (i0 % kSlots) * kSlotFloats;
+        const int cnt0 = min(kRingNnz, len - s0 * kRingNnz);
+        float first[kRingNnz];
+        if (cnt0 == kRingNnz) {
+            const unsigned base = (unsigned)__cvta_generic_to_shared(slot0);
+#pragma unroll
+            for (int j = 0; j < kRingNnz; ++j) first[j] = lds_pinned(base + (j * 32 + lane) * 4);
+            if (!UNIT) {
+#pragma unroll
+                for (int j4 = 0; j4 < kRingNnz; j4 += 4) {
+                    const float4 v = lds4_pinned(base + (kRingNnz * 32 + j4) * 4);
+                    first[j4 + 0] = __fmul_rn(v.x, first[j4 + 0]);
+                    first[j4 + 1] = __fmul_rn(v.y, first[j4 + 1]);
+                    first[j4 + 2] = __fmul_rn(v.z, first[j4 + 2]);
+                    first[j4 + 3] = __fmul_rn(v.w, first[j4 + 3]);
+                }
+            }
+        }
         float acc = 0.f;
-        if (s > 0) {
+        if (s0 > 0) {
             asm volatile("bar.sync %0, 64;\n" ::"r"(bar_prev) : "memory");
             acc = sums[lane];
         }
-        const float* slot = ring + (i % kRingStages) * kSlotFloats;
-        const int cnt = min(kRingNnz, len - s * kRingNnz);
-        if (cnt == kRingNnz) {
-            acc = drain_full_slot<UNIT>(acc, slot, lane);
+        if (cnt0 == kRingNnz) {
+#pragma unroll
+            for (int j = 0; j < kRingNnz; ++j) acc = __fadd_rn(acc, first[j]);
         } else if (UNIT) {
-            for (int j = 0; j < cnt; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
+            for (int j = 0; j < cnt0; ++j) acc = __fadd_rn(acc, slot0[j * 32 + lane]);
         } else {
-            for (int j = 0; j < cnt; ++j)
-                acc = fg::mul_then_add(acc, slot[kRingNnz * 32 + j], slot[j * 32 + lane]);
+            for (int j = 0; j < cnt0; ++j)
+                acc = fg::mul_then_add(acc, slot0[kRingNnz * 32 + j], slot0[j * 32 + lane]);
         }
-        if (s + 1 < n_stages) {
+#pragma unroll
+        for (int u = 1; u < TURN; ++u) {
+            const int cnt = min(kRingNnz, len - (s0 + u) * kRingNnz);  // <= 0 past the row's end
+            const float* slot = ring + ((i0 + u) % kSlots) * kSlotFloats;
+            if (cnt == kRingNnz) {
+                acc = drain_full_slot<UNIT>(acc, slot, lane);
+            } else if (UNIT) {
+                for (int j = 0; j < cnt; ++j) acc = __fadd_rn(acc, slot[j * 32 + lane]);
+            } else {
+                for (int j = 0; j < cnt; ++j)
+                    acc = fg::mul_then_add(acc, slot[kRingNnz * 32 + j], slot[j * 32 + lane]);
+            }
+        }
+        if (s0 + TURN < n_stages) {  // another turn follows
             sums[lane] = acc;
             __threadfence_block();
             asm volatile("bar.arrive %0, 64;\n" ::"r"(bar_mine) : "memory");
         } else if (col0 + lane < a.d) {
-            a.out[(int64_t)row * a.ldo + col0 + lane] = acc;  // the row's last stage
+            a.out[(int64_t)row * a.ldo + col0 + lane] = acc;  // the row's last turn
         }
-        __syncwarp();  // every lane has read the slot
-        // refill the slot just drained, off the chain of turns
-        fill(i + kRingStages, c_next, v_next);
-        c_next = c_after;
-        v_next = v_after;
-        fetch_ids(i + kRingStages + 2, c_after, v_after);
+        __syncwarp();  // every lane has read the slots
+        // refill the slots just drained, off the chain of turns
+#pragma unroll
+        for (int u = 0; u < TURN; ++u) {
+            fill(i0 + kSlots + u, c_next[u], v_next[u]);
+            c_next[u] = c_after[u];
+            v_next[u] = v_after[u];
+            fetch_ids(i0 + kSlots + 2 * TURN + u, c_after[u], v_after[u]);
+        }
     }
 }
 
@@ -477,23 +526,38 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
 //   spmm_rows_kernel       streams gathers at about 17 TB/s, about 75 ns per nonzero of one row
 //                          (8 gathers per L2 round trip): a 20,000-nonzero row alone takes 1.5 ms;
 //   spmm_long_rows_kernel  about 13 TB/s (every slice crosses shared memory twice), 15 ns per nonzero;
-//   spmm_heavy_rows_kernel about 9 TB/s (a block's warps take turns), 7 ns per nonzero.
+//   spmm_heavy_rows_kernel with 4 warps per block about 9 TB/s and 7 ns per nonzero, with 8 warps
+//                          about 6 TB/s and 5 ns (more time for a warp to refill between turns).
 // Units run tile-major, so a kernel's longest rows are met again in its last feature tile: alone, a
 // kernel takes
 //     (1 - 1/tiles) * bytes / rate  +  max(bytes / rate / tiles, longest row's time).
-// Run one after the other, the launch takes the sum of the parts.  Run side by side (heavy then long
-// rows on a second stream, see spmm_dispatch) the streams share the path from L2, and the launch is
-// modelled as the largest of: all bytes one after the other, and each stream's own time with its
-// streaming parts stretched to that sum.  Every pair of candidate thresholds is tried and the
+// Run one after the other, the launch takes the sum of the parts.  Run side by side (each kernel on
+// a stream of its own, see spmm_dispatch) they share the path from L2, and the launch is modelled
+// as the largest of: all bytes one after the other, and each kernel's own time with its streaming
+// part stretched to that sum.  Every pair of candidate thresholds is tried and the
 // cheapest wins.  A threshold fixed at schedule creation overrides the choice.  The choice never
 // affects a result bit.
 constexpr double kRowsRate = 17e12, kRowsSecPerNnz = 75e-9;
 constexpr double kRingRate = 13e12, kRingSecPerNnz = 15e-9;
-constexpr double kHeavyRate = 9e12, kHeavySecPerNnz = 7.5e-9;
+constexpr double kHeavyRate[2] = {9e12, 6e12}, kHeavySecPerNnz[2] = {7.5e-9, 5e-9};  // 4 / 8 warps
+
+int sm_count() {
+    static thread_local int n = 0;
+    if (n == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+            n = v;
+        else
+            n = 148;
+    }
+    return n;
+}
 
 struct RowSplit {
     int64_t heavy = 0;  // order[0, heavy): spmm_heavy_rows_kernel
     int64_t ring = 0;   // order[heavy, ring): spmm_long_rows_kernel; the rest: spmm_rows_kernel
+    bool wide = false;  // heavy rows with 8 warps per block instead of 4
 };
 
 RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, bool side_by_side) {
@@ -501,6 +565,7 @@ RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, boo
     if (sch.fixed_threshold > 0) {
         best_split.heavy = sch.fixed_heavy_rows;
         best_split.ring = sch.fixed_rows;
+        best_split.wide = sch.fixed_wide;
         return best_split;
     }
     const double short_tiles = (d + short_tile - 1) / short_tile;
@@ -511,37 +576,46 @@ RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, boo
         return stream <= 0.0 ? 0.0 : stream * (1.0 - 1.0 / tiles) + fmax(stream / tiles, row_time);
     };
     // thresholds t_heavy >= t_ring; "none" is a threshold above the longest row
-    auto estimate = [&](double nnz_heavy, double t_heavy, double nnz_ring_up, double t_ring) {
+    auto estimate = [&](double nnz_heavy, double t_heavy, double nnz_ring_up, double t_ring, int wide) {
         const double nnz_ring = nnz_ring_up - nnz_heavy, nnz_rows = (double)sch.nnz - nnz_ring_up;
-        const double s_heavy = nnz_heavy * long_bytes / kHeavyRate;
+        const double s_heavy = nnz_heavy * long_bytes / kHeavyRate[wide];
         const double s_ring = nnz_ring * long_bytes / kRingRate;
         const double s_rows = nnz_rows * short_bytes / kRowsRate;
-        const double heavy_row = longest * kHeavySecPerNnz;
+        const double heavy_row = longest * kHeavySecPerNnz[wide];
         const double ring_row = fmin(t_heavy, longest) * kRingSecPerNnz;
         const double rows_row = fmin(t_ring, longest) * kRowsSecPerNnz;
         if (!side_by_side)
             return part(s_heavy, long_tiles, heavy_row) + part(s_ring, long_tiles, ring_row) +
                    part(s_rows, short_tiles, rows_row);
+        // three streams side by side: each kernel's streaming part stretched to the time of all bytes
         const double all = s_heavy + s_ring + s_rows;
-        const double stretch = s_heavy + s_ring > 0.0 ? all / (s_heavy + s_ring) : 1.0;
-        const double side = part(s_heavy * stretch, long_tiles, heavy_row) + part(s_ring * stretch, long_tiles, ring_row);
-        const double main = s_rows > 0.0 ? part(all, short_tiles, rows_row) : 0.0;
-        return fmax(all, fmax(side, main));
+        double t = all;
+        if (s_heavy > 0.0) t = fmax(t, part(all, long_tiles, heavy_row));
+        if (s_ring > 0.0) t = fmax(t, part(all, long_tiles, ring_row));
+        if (s_rows > 0.0) t = fmax(t, part(all, short_tiles, rows_row));
+        return t;
     };
     const double none = longest + 1.0;
-    double best = estimate(0.0, none, 0.0, none);
+    double best = estimate(0.0, none, 0.0, none, 0);
     for (int lr = 0; lr < fg::kSplitLevels; ++lr) {  // ring threshold
         if (sch.rows_at_least[lr] == 0) break;
         const double t_ring = (double)fg::split_threshold(lr);
         for (int lh = lr; lh <= fg::kSplitLevels; ++lh) {  // heavy threshold, kSplitLevels = none
             const bool no_heavy = lh == fg::kSplitLevels || sch.rows_at_least[lh] == 0;
-            const double t = no_heavy ? estimate(0.0, none, (double)sch.nnz_at_least[lr], t_ring)
-                                      : estimate((double)sch.nnz_at_least[lh], (double)fg::split_threshold(lh),
-                                                 (double)sch.nnz_at_least[lr], t_ring);
-            if (t < best) {
-                best = t;
-                best_split.heavy = no_heavy ? 0 : sch.rows_at_least[lh];
-                best_split.ring = sch.rows_at_least[lr];
+            // the 8-warp form only where all its blocks are resident at once (two per SM): it is
+            // there for a handful of hub rows, not for throughput
+            const bool wide_ok = !no_heavy && (double)sch.rows_at_least[lh] * long_tiles <= 2.0 * sm_count();
+            for (int wide = 0; wide < (wide_ok ? 2 : 1); ++wide) {
+                const double t =
+                    no_heavy ? estimate(0.0, none, (double)sch.nnz_at_least[lr], t_ring, 0)
+                             : estimate((double)sch.nnz_at_least[lh], (double)fg::split_threshold(lh),
+                                        (double)sch.nnz_at_least[lr], t_ring, wide);
+                if (t < best) {
+                    best = t;
+                    best_split.heavy = no_heavy ? 0 : sch.rows_at_least[lh];
+                    best_split.ring = sch.rows_at_least[lr];
+                    best_split.wide = wide != 0;
+                }
             }
             if (no_heavy) break;
         }
@@ -549,30 +623,32 @@ RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, boo
     return best_split;
 }
 
-// A second stream (per host thread and device) on which the long-row kernel can run beside
-// spmm_rows_kernel.  Fork and join are event waits on the device: the caller's stream sees one
-// call that is complete when both kernels are, also under stream capture.
+// Two more streams (per host thread and device) on which the heavy-row and the long-row kernel can
+// run beside spmm_rows_kernel.  Fork and join are event waits on the device: the caller's stream
+// sees one call that is complete when all kernels are, also under stream capture.
 struct SideStream {
     int device = -1;
-    cudaStream_t stream = nullptr;
-    cudaEvent_t fork = nullptr, join = nullptr;
+    cudaStream_t heavy = nullptr, ring = nullptr;
+    cudaEvent_t fork = nullptr, join_heavy = nullptr, join_ring = nullptr;
     bool prepare() {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess) return false;
         if (dev != device) {  // a thread that moves to another device gets fresh objects there
-            stream = nullptr;
-            fork = join = nullptr;
+            heavy = ring = nullptr;
+            fork = join_heavy = join_ring = nullptr;
             device = dev;
         }
-        if (!stream) {
+        if (!heavy) {
             int least = 0, greatest = 0;
             cudaDeviceGetStreamPriorityRange(&least, &greatest);
             // highest priority: the heaviest rows bound the launch, their blocks go first
-            if (cudaStreamCreateWithPriority(&stream, cudaStreamNonBlocking, greatest) != cudaSuccess ||
+            if (cudaStreamCreateWithPriority(&heavy, cudaStreamNonBlocking, greatest) != cudaSuccess ||
+                cudaStreamCreateWithPriority(&ring, cudaStreamNonBlocking, greatest) != cudaSuccess ||
                 cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&join, cudaEventDisableTiming) != cudaSuccess) {
+                cudaEventCreateWithFlags(&join_heavy, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&join_ring, cudaEventDisableTiming) != cudaSuccess) {
                 (void)cudaGetLastError();
-                stream = nullptr;
+                heavy = ring = nullptr;
                 return false;
             }
         }
@@ -605,24 +681,23 @@ int launch_long(const SpmmArgs& a, cudaStream_t s) {
     return FG_OK;
 }
 
-template <bool UNIT, int W>
+template <bool UNIT, int W, int TURN>
 int launch_heavy_w(const SpmmArgs& a, cudaStream_t s) {
     const int64_t blocks = (int64_t)a.n_sched * a.n_tiles;
     if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
     if (blocks == 0) return FG_OK;
-    static_assert(heavy_smem_bytes<W>() <= 227 * 1024, "rings do not fit in shared memory");
-    FG_CUDA_TRY(cudaFuncSetAttribute(spmm_heavy_rows_kernel<UNIT, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     heavy_smem_bytes<W>()));
-    spmm_heavy_rows_kernel<UNIT, W><<<(unsigned)blocks, W * 32, heavy_smem_bytes<W>(), s>>>(a);
+    static_assert(heavy_smem_bytes<W, TURN>() <= 227 * 1024, "rings do not fit in shared memory");
+    FG_CUDA_TRY(cudaFuncSetAttribute(spmm_heavy_rows_kernel<UNIT, W, TURN>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, heavy_smem_bytes<W, TURN>()));
+    spmm_heavy_rows_kernel<UNIT, W, TURN><<<(unsigned)blocks, W * 32, heavy_smem_bytes<W, TURN>(), s>>>(a);
     FG_CUDA_TRY(cudaGetLastError());
     fg::count_launches(1);
     return FG_OK;
 }
 
-constexpr int kHeavyWarps = 4;  // 8 warps: the same time per row, lower throughput (5.7 against 9 TB/s)
-
-int launch_heavy(const SpmmArgs& a, cudaStream_t s) {
-    return a.vals == nullptr ? launch_heavy_w<true, kHeavyWarps>(a, s) : launch_heavy_w<false, kHeavyWarps>(a, s);
+int launch_heavy(const SpmmArgs& a, bool wide, cudaStream_t s) {
+    if (wide) return a.vals == nullptr ? launch_heavy_w<true, 8, 1>(a, s) : launch_heavy_w<false, 8, 1>(a, s);
+    return a.vals == nullptr ? launch_heavy_w<true, 4, 1>(a, s) : launch_heavy_w<false, 4, 1>(a, s);
 }
 
 template <int G, int VEC>
@@ -747,40 +822,50 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
         a.order_begin = (int32_t)split.ring;
         a.n_sched = (int32_t)(n_rows - split.ring);
         // the kernels write disjoint rows
-        forked = side_by_side && a.n_sched > 0 && side.prepare() &&
-                 cudaEventRecord(side.fork, s) == cudaSuccess &&
-                 cudaStreamWaitEvent(side.stream, side.fork, 0) == cudaSuccess;
-        cudaStream_t ls = forked ? side.stream : s;
+        forked = side_by_side && side.prepare() && cudaEventRecord(side.fork, s) == cudaSuccess &&
+                 cudaStreamWaitEvent(side.heavy, side.fork, 0) == cudaSuccess &&
+                 cudaStreamWaitEvent(side.ring, side.fork, 0) == cudaSuccess;
         SpmmArgs h = a;
         h.n_tiles = (d + 31) / 32;
         h.order_begin = 0;
         h.n_sched = (int32_t)split.heavy;
-        int rc = launch_heavy(h, ls);
+        int rc = launch_heavy(h, split.wide, forked ? side.heavy : s);
         if (rc == FG_OK) {
             h.order_begin = (int32_t)split.heavy;
             h.n_sched = (int32_t)(split.ring - split.heavy);
-            rc = launch_long(h, ls);
+            rc = launch_long(h, forked ? side.ring : s);
         }
-        // record the join point even after a failed launch: the side stream must come back to the
+        // record the join points even after a failed launch: the side streams must come back to the
         // caller's stream (a capture could not end otherwise)
-        if (forked) FG_CUDA_TRY(cudaEventRecord(side.join, side.stream));
-        if (rc != FG_OK || a.n_sched == 0) {
-            if (forked) FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join, 0));
+        if (forked) {
+            FG_CUDA_TRY(cudaEventRecord(side.join_heavy, side.heavy));
+            FG_CUDA_TRY(cudaEventRecord(side.join_ring, side.ring));
+        }
+        if (rc != FG_OK) {
+            if (forked) {
+                FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_heavy, 0));
+                FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_ring, 0));
+            }
             return rc;
         }
     }
     a.n_tiles = (d + tile - 1) / tile;
-    int rc;
-    switch (tile / 4) {
-        case 1: rc = launch<1, 4>(a, dds, s); break;
-        case 2: rc = launch<2, 4>(a, dds, s); break;
-        case 4: rc = launch<4, 4>(a, dds, s); break;
-        case 8: rc = launch<8, 4>(a, dds, s); break;
-        case 16: rc = launch<16, 4>(a, dds, s); break;
-        default: rc = launch<32, 4>(a, dds, s); break;
+    int rc = FG_OK;
+    if (a.n_sched > 0) {
+        switch (tile / 4) {
+            case 1: rc = launch<1, 4>(a, dds, s); break;
+            case 2: rc = launch<2, 4>(a, dds, s); break;
+            case 4: rc = launch<4, 4>(a, dds, s); break;
+            case 8: rc = launch<8, 4>(a, dds, s); break;
+            case 16: rc = launch<16, 4>(a, dds, s); break;
+            default: rc = launch<32, 4>(a, dds, s); break;
+        }
     }
-    // join: work enqueued on the caller's stream after this call waits for the long rows too
-    if (forked) FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join, 0));
+    // join: work enqueued on the caller's stream after this call waits for the other kernels too
+    if (forked) {
+        FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_heavy, 0));
+        FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_ring, 0));
+    }
     return rc;
 }
 

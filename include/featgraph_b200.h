@@ -71,7 +71,9 @@ typedef struct fg_row_schedule fg_row_schedule;
 /* d_indptr: n_rows+1 ascending positions.  long_row_threshold: 0 = each SpMM launch decides
  * which rows count as long and which as heavy (see fg_spmm_csr_f32); > 0 fixes it: rows with at
  * least that many nonzeros always take the long-row kernel, rows with at least 16 times as many
- * the heavy-row kernel (INT32_MAX = none ever do).  Synchronises `stream` before returning. */
+ * the heavy-row kernel (INT32_MAX = none ever do); < 0 fixes |long_row_threshold| in the same way
+ * and selects the 8-warp form of the heavy-row kernel instead of the 4-warp one.  Every setting
+ * gives the same result bits.  Synchronises `stream` before returning. */
 int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long_row_threshold,
                            void* stream, fg_row_schedule** out_schedule);
 /* Device pointer to the n_rows row ids in visiting order (valid until destroy). */

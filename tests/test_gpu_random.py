@@ -39,7 +39,7 @@ def test_random_cases(oracle, seed):
         x = (rng.random((n_cols, d), dtype=np.float32) * 2 - 1).astype(np.float32)
         y = (rng.random((n_rows, d), dtype=np.float32) * 2 - 1).astype(np.float32)
         tile = int(rng.choice([0, 0, 4, 16, 32, 64, 128]))
-        threshold = int(rng.choice([0, 0, 1, 64, 700, 2 ** 31 - 1]))
+        threshold = int(rng.choice([0, 0, 1, 64, 700, 2 ** 31 - 1, -1, -8]))
         tag = "seed=%d %dx%d nnz=%d d=%d %s unit=%s tile=%d thr=%d" % (seed, n_rows, n_cols, adj.nnz, d, kind, unit,
                                                                    tile, threshold)
         want = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)

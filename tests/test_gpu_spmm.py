@@ -155,7 +155,7 @@ def test_heavy_rows_take_the_block_per_row_kernel_and_stay_exact(oracle, d, unit
         a.data = (np.random.default_rng(302).random(a.nnz, dtype=np.float32) * 2 - 1).astype(np.float32)
     x = graphgen.uniform_features((30000, d), seed=303 + d)
     want = oracle.spmm_csr(a.indptr, a.indices, a.data, x)
-    for threshold in (1, 2, 8, 64):  # heavy from 16, 32, 128, 1024 nonzeros
+    for threshold in (1, 2, 8, 64, -1, -4, -64):  # heavy from 16, 32, 128, 1024 nonzeros; < 0: 8 warps per row
         got = G.spmm_csr(a.indptr, a.indices, None if unit else a.data, x, long_row_threshold=threshold)
         np.testing.assert_array_equal(got, want, err_msg="threshold %d" % threshold)
 
