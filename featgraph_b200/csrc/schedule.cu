@@ -24,6 +24,16 @@ __global__ void degree_keys_kernel(const int32_t* __restrict__ indptr, int64_t n
     }
 }
 
+__global__ void row_extents_kernel(const int32_t* __restrict__ indptr, const int32_t* __restrict__ order,
+                                   int64_t n_rows, int2* __restrict__ extent) {
+    const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < n_rows) {
+        const int32_t r = order[p];
+        const int32_t start = indptr[r];
+        extent[p] = make_int2(start, indptr[r + 1] - start);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -68,11 +78,13 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
                           "%s failed: %s", #expr, cudaGetErrorString(e__));                \
             cleanup();                                                                     \
             cudaFree(sch->d_order);                                                        \
+            cudaFree(sch->d_extent);                                                       \
             delete sch;                                                                    \
             return rc;                                                                     \
         }                                                                                  \
     } while (0)
     FG_TRY_OR_CLEAN(cudaMalloc(&sch->d_order, sizeof(int32_t) * n_rows));
+    FG_TRY_OR_CLEAN(cudaMalloc(&sch->d_extent, sizeof(int2) * n_rows));
     FG_TRY_OR_CLEAN(cudaMalloc(&keys_in, sizeof(uint32_t) * n_rows));
     FG_TRY_OR_CLEAN(cudaMalloc(&keys_out, sizeof(uint32_t) * n_rows));
     FG_TRY_OR_CLEAN(cudaMalloc(&rows_in, sizeof(int32_t) * n_rows));
@@ -86,6 +98,8 @@ int fg_row_schedule_create(const int32_t* d_indptr, int64_t n_rows, int32_t long
     FG_TRY_OR_CLEAN(cudaMalloc(&temp, temp_bytes ? temp_bytes : 1));
     FG_TRY_OR_CLEAN(cub::DeviceRadixSort::SortPairsDescending(
         temp, temp_bytes, keys_in, keys_out, rows_in, sch->d_order, (int)n_rows, 0, 32, s));
+    row_extents_kernel<<<blocks, threads, 0, s>>>(d_indptr, sch->d_order, n_rows, sch->d_extent);
+    FG_TRY_OR_CLEAN(cudaGetLastError());
     // the sorted nonzero counts come back once; the split statistics are computed on the host
     h_keys.resize((size_t)n_rows);
     FG_TRY_OR_CLEAN(cudaMemcpyAsync(h_keys.data(), keys_out, sizeof(uint32_t) * n_rows,
@@ -143,6 +157,7 @@ int64_t fg_row_schedule_rows_at_least(const fg_row_schedule* schedule, int64_t m
 void fg_row_schedule_destroy(fg_row_schedule* schedule) {
     if (!schedule) return;
     cudaFree(schedule->d_order);
+    cudaFree(schedule->d_extent);
     delete schedule;
 }
 

@@ -2,6 +2,8 @@
 #pragma once
 #include <cstdint>
 
+#include <cuda_runtime.h>
+
 namespace fg {
 constexpr int kSplitLevels = 16;  // candidate long-row thresholds 64, 128, ..., 2^21
 inline int64_t split_threshold(int level) { return (int64_t)64 << level; }
@@ -10,6 +12,9 @@ constexpr int64_t kFixedHeavyFactor = 16;
 
 struct fg_row_schedule {
     int32_t* d_order = nullptr;  // row ids, nonzero count descending, ties in row order
+    // (first nonzero, nonzero count) of row d_order[p], at position p: a kernel that walks the order reads
+    // a row's extent with one coalesced load instead of two dependent ones through the row id
+    int2* d_extent = nullptr;
     int64_t n_rows = 0;
     int64_t nnz = 0;
     int64_t max_row_nnz = 0;

@@ -45,6 +45,7 @@ struct SpmmArgs {
     const float* x;
     float* out;
     const int32_t* order;  // row visiting order or nullptr
+    const int2* extent;    // (first nonzero, count) of row order[p] at position p, or nullptr (CSR only)
     int32_t order_begin;   // this launch covers order[order_begin, order_begin + n_sched)
     int32_t n_sched;
     int32_t n_rows;
@@ -96,9 +97,12 @@ struct Slice<1> {
 
 // G lanes per (row, tile) unit; VEC floats per lane; DDS selects the two-level sum; UNIT: every
 // adjacency value is 1.0 (no value array is read, and 1.0 * x == x exactly, so nothing is multiplied).
-template <int G, int VEC, bool DDS, bool UNIT>
-__global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a) {
-    constexpr int CH = G < 8 ? G : 8;  // gathers issued back to back
+// SHORT: the form for rows of a few nonzeros, where what counts is how many rows an SM has in
+// flight, not how many gathers a row has: 4 gathers back to back and 6 blocks per SM instead of 8 and 4.
+template <int G, int VEC, bool DDS, bool UNIT, bool SHORT>
+__global__ void __launch_bounds__(kThreads, SHORT ? 6 : 4) spmm_rows_kernel(const SpmmArgs a) {
+    constexpr int CHMAX = SHORT ? 4 : 8;
+    constexpr int CH = G < CHMAX ? G : CHMAX;  // gathers issued back to back
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
     const int64_t unit = (int64_t)blockIdx.x * (kThreads / G) + (threadIdx.x / G);
@@ -106,10 +110,12 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
     const bool live = unit < n_units;
 
     int row = 0, tile = 0;
+    int2 extent = make_int2(0, 0);
     if (live) {
         tile = (int)(unit / a.n_sched);
         const int p = a.order_begin + (int)(unit - (int64_t)tile * a.n_sched);
         row = a.order ? a.order[p] : p;
+        if (!DDS && a.extent) extent = a.extent[p];
     }
     const int col = tile * (G * VEC) + lig * VEC;
     const bool col_ok = live && col < a.d;
@@ -119,8 +125,8 @@ __global__ void __launch_bounds__(kThreads, 4) spmm_rows_kernel(const SpmmArgs a
     total.zero();
 
     for (int k = 0; k < (DDS ? a.parts : 1); ++k) {
-        int start = 0, len = 0;
-        if (live) {
+        int start = extent.x, len = extent.y;
+        if (live && (DDS || !a.extent)) {
             const int32_t* p = a.pos + (int64_t)k * ((int64_t)a.n_rows + 1) + row;
             start = p[0];
             len = p[1] - start;
@@ -623,36 +629,53 @@ RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, boo
     return best_split;
 }
 
-// Two more streams (per host thread and device) on which the heavy-row and the long-row kernel can
-// run beside spmm_rows_kernel.  Fork and join are event waits on the device: the caller's stream
-// sees one call that is complete when all kernels are, also under stream capture.
+// Three more streams (per host thread and device) on which the heavy-row, the long-row and the
+// short-row kernel can run beside spmm_rows_kernel.  Fork and join are event waits on the device:
+// the caller's stream sees one call that is complete when all kernels are, also under stream capture.
 struct SideStream {
+    enum { kHeavy = 0, kRing = 1, kShort = 2, kStreams = 3 };
     int device = -1;
-    cudaStream_t heavy = nullptr, ring = nullptr;
-    cudaEvent_t fork = nullptr, join_heavy = nullptr, join_ring = nullptr;
+    cudaStream_t stream[kStreams] = {nullptr, nullptr, nullptr};
+    cudaEvent_t fork = nullptr, join[kStreams] = {nullptr, nullptr, nullptr};
     bool prepare() {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess) return false;
         if (dev != device) {  // a thread that moves to another device gets fresh objects there
-            heavy = ring = nullptr;
-            fork = join_heavy = join_ring = nullptr;
+            for (int i = 0; i < kStreams; ++i) stream[i] = nullptr, join[i] = nullptr;
+            fork = nullptr;
             device = dev;
         }
-        if (!heavy) {
+        if (!fork) {
             int least = 0, greatest = 0;
             cudaDeviceGetStreamPriorityRange(&least, &greatest);
-            // highest priority: the heaviest rows bound the launch, their blocks go first
-            if (cudaStreamCreateWithPriority(&heavy, cudaStreamNonBlocking, greatest) != cudaSuccess ||
-                cudaStreamCreateWithPriority(&ring, cudaStreamNonBlocking, greatest) != cudaSuccess ||
-                cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&join_heavy, cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&join_ring, cudaEventDisableTiming) != cudaSuccess) {
+            bool ok = cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) == cudaSuccess;
+            for (int i = 0; ok && i < kStreams; ++i)
+                // the heaviest rows bound the launch: their blocks go first
+                ok = cudaStreamCreateWithPriority(&stream[i], cudaStreamNonBlocking,
+                                                  i == kShort ? least : greatest) == cudaSuccess &&
+                     cudaEventCreateWithFlags(&join[i], cudaEventDisableTiming) == cudaSuccess;
+            if (!ok) {
                 (void)cudaGetLastError();
-                heavy = ring = nullptr;
+                fork = nullptr;
                 return false;
             }
         }
         return true;
+    }
+    // every side stream starts after what the caller's stream holds so far
+    bool fork_from(cudaStream_t s) {
+        if (!prepare() || cudaEventRecord(fork, s) != cudaSuccess) return false;
+        for (int i = 0; i < kStreams; ++i)
+            if (cudaStreamWaitEvent(stream[i], fork, 0) != cudaSuccess) return false;
+        return true;
+    }
+    // and the caller's stream continues after all of them
+    int join_to(cudaStream_t s) {
+        for (int i = 0; i < kStreams; ++i) {
+            FG_CUDA_TRY(cudaEventRecord(join[i], stream[i]));
+            FG_CUDA_TRY(cudaStreamWaitEvent(s, join[i], 0));
+        }
+        return FG_OK;
     }
 };
 
@@ -700,7 +723,7 @@ int launch_heavy(const SpmmArgs& a, bool wide, cudaStream_t s) {
     return a.vals == nullptr ? launch_heavy_w<true, 4, 1>(a, s) : launch_heavy_w<false, 4, 1>(a, s);
 }
 
-template <int G, int VEC>
+template <int G, int VEC, bool SHORT = false>
 int launch(const SpmmArgs& a, bool dds, cudaStream_t s) {
     const int64_t n_units = (int64_t)a.n_sched * a.n_tiles;
     const int64_t units_per_block = kThreads / G;
@@ -708,17 +731,34 @@ int launch(const SpmmArgs& a, bool dds, cudaStream_t s) {
     if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
     if (blocks == 0) return FG_OK;
     const bool unit = a.vals == nullptr;
-    if (dds && unit)
-        spmm_rows_kernel<G, VEC, true, true><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+    if (SHORT) {  // CSR only
+        if (unit)
+            spmm_rows_kernel<G, VEC, false, true, SHORT><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+        else
+            spmm_rows_kernel<G, VEC, false, false, SHORT><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+    } else if (dds && unit)
+        spmm_rows_kernel<G, VEC, true, true, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
     else if (dds)
-        spmm_rows_kernel<G, VEC, true, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+        spmm_rows_kernel<G, VEC, true, false, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
     else if (unit)
-        spmm_rows_kernel<G, VEC, false, true><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+        spmm_rows_kernel<G, VEC, false, true, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
     else
-        spmm_rows_kernel<G, VEC, false, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
+        spmm_rows_kernel<G, VEC, false, false, false><<<(unsigned)blocks, kThreads, 0, s>>>(a);
     FG_CUDA_TRY(cudaGetLastError());
     fg::count_launches(1);
     return FG_OK;
+}
+
+template <bool SHORT>
+int launch_tile(const SpmmArgs& a, int tile, bool dds, cudaStream_t s) {
+    switch (tile / 4) {
+        case 1: return launch<1, 4, SHORT>(a, dds, s);
+        case 2: return launch<2, 4, SHORT>(a, dds, s);
+        case 4: return launch<4, 4, SHORT>(a, dds, s);
+        case 8: return launch<8, 4, SHORT>(a, dds, s);
+        case 16: return launch<16, 4, SHORT>(a, dds, s);
+        default: return launch<32, 4, SHORT>(a, dds, s);
+    }
 }
 
 // The share of L2 in which a gathered slice of x stays resident under all-SM random access.
@@ -785,6 +825,7 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     a.x = x;
     a.out = out;
     a.order = schedule ? fg_row_schedule_order(schedule) : nullptr;
+    a.extent = (schedule && !dds) ? schedule->d_extent : nullptr;
     a.order_begin = 0;
     a.n_sched = (int32_t)n_rows;
     a.n_rows = (int32_t)n_rows;
@@ -816,55 +857,45 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     const bool side_by_side = !slice_can_stay_in_l2(n_cols);
     RowSplit split;
     if (schedule && !dds) split = choose_row_split(*schedule, d, tile, side_by_side);
-    bool forked = false;
+    // Rows of fewer than 64 nonzeros (the schedule's first threshold) take the SHORT form of the
+    // rows kernel, launched last (in side-by-side mode on a stream of its own).
+    int64_t first_short = n_rows;
+    if (schedule && !dds) {
+        first_short = schedule->rows_at_least[0];
+        if (first_short < split.ring) first_short = split.ring;
+    }
     SideStream& side = side_stream();
-    if (split.ring > 0) {
-        a.order_begin = (int32_t)split.ring;
-        a.n_sched = (int32_t)(n_rows - split.ring);
-        // the kernels write disjoint rows
-        forked = side_by_side && side.prepare() && cudaEventRecord(side.fork, s) == cudaSuccess &&
-                 cudaStreamWaitEvent(side.heavy, side.fork, 0) == cudaSuccess &&
-                 cudaStreamWaitEvent(side.ring, side.fork, 0) == cudaSuccess;
+    const bool forked = side_by_side && (split.ring > 0 || first_short < n_rows) && side.fork_from(s);
+    auto stream_for = [&](int which) { return forked ? side.stream[which] : s; };
+    int rc = FG_OK;
+    {
         SpmmArgs h = a;
         h.n_tiles = (d + 31) / 32;
         h.order_begin = 0;
         h.n_sched = (int32_t)split.heavy;
-        int rc = launch_heavy(h, split.wide, forked ? side.heavy : s);
+        rc = launch_heavy(h, split.wide, stream_for(SideStream::kHeavy));
         if (rc == FG_OK) {
             h.order_begin = (int32_t)split.heavy;
             h.n_sched = (int32_t)(split.ring - split.heavy);
-            rc = launch_long(h, forked ? side.ring : s);
-        }
-        // record the join points even after a failed launch: the side streams must come back to the
-        // caller's stream (a capture could not end otherwise)
-        if (forked) {
-            FG_CUDA_TRY(cudaEventRecord(side.join_heavy, side.heavy));
-            FG_CUDA_TRY(cudaEventRecord(side.join_ring, side.ring));
-        }
-        if (rc != FG_OK) {
-            if (forked) {
-                FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_heavy, 0));
-                FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_ring, 0));
-            }
-            return rc;
+            rc = launch_long(h, stream_for(SideStream::kRing));
         }
     }
     a.n_tiles = (d + tile - 1) / tile;
-    int rc = FG_OK;
-    if (a.n_sched > 0) {
-        switch (tile / 4) {
-            case 1: rc = launch<1, 4>(a, dds, s); break;
-            case 2: rc = launch<2, 4>(a, dds, s); break;
-            case 4: rc = launch<4, 4>(a, dds, s); break;
-            case 8: rc = launch<8, 4>(a, dds, s); break;
-            case 16: rc = launch<16, 4>(a, dds, s); break;
-            default: rc = launch<32, 4>(a, dds, s); break;
-        }
+    if (rc == FG_OK) {
+        a.order_begin = (int32_t)split.ring;
+        a.n_sched = (int32_t)(first_short - split.ring);
+        rc = launch_tile<false>(a, tile, dds, s);
     }
-    // join: work enqueued on the caller's stream after this call waits for the other kernels too
+    if (rc == FG_OK && first_short < n_rows) {
+        a.order_begin = (int32_t)first_short;
+        a.n_sched = (int32_t)(n_rows - first_short);
+        rc = launch_tile<true>(a, tile, dds, stream_for(SideStream::kShort));
+    }
+    // join even after a failed launch: the side streams must come back to the caller's stream (a
+    // capture could not end otherwise); work enqueued on it afterwards waits for all kernels
     if (forked) {
-        FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_heavy, 0));
-        FG_CUDA_TRY(cudaStreamWaitEvent(s, side.join_ring, 0));
+        const int rcj = side.join_to(s);
+        if (rc == FG_OK) rc = rcj;
     }
     return rc;
 }
@@ -1006,6 +1037,7 @@ int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, co
     view.n_rows = n_rows;
     view.fixed_threshold = INT32_MAX;
     view.fixed_rows = 0;
+    view.rows_at_least[0] = n_rows;  // no degree statistics here: one kernel form for all rows, no side streams
     return spmm_dispatch(&view, d_indptr, d_indices, d_vals, d_x, d, d_out, d, n_rows, n_cols, nnz, d,
                          1, feat_tile, stream, false);
 }
