@@ -6,8 +6,11 @@ SpMM: rank p owns rows ``[bounds[p], bounds[p+1])`` of the adjacency and the sam
 feature matrix.  A call all-gathers the feature rows into every rank's own memory (the one
 exchange step the op has), then runs the single-GPU kernel on the local rows; the output stays
 sharded.  No row is ever split, so each output element is summed exactly as on one GPU.
-Row blocks differ in size, so the gather runs over equal slots of a padded buffer (one plain
-all-gather) and each shard's column ids are remapped once, at construction, to point into it.
+Row blocks differ in size.  Where they differ little (a graph whose rows are of similar weight) the
+gather runs over equal slots of a padded buffer (one plain all-gather) and each shard's column ids
+are remapped once, at construction, to point into it.  Where they differ much (nnz-balanced ranges
+of an R-MAT graph: a few hub rows on one rank, a million light rows on another) padding would
+multiply the bytes exchanged, so the blocks are gathered at their own sizes into the plain matrix.
 
 SDDMM: rank p owns the edges of its rows (a contiguous range of the CSR-ordered edge list).  The
 row-side features are local, the column-side features are all-gathered; the per-edge output
@@ -35,12 +38,17 @@ def shard_csr_rows(adj_csr, bounds, rank):
     return local
 
 
-def all_gather_rows(full, local, bounds, group=None):
+class ExchangeError(RuntimeError):
+    """The feature all-gather failed or timed out (a peer rank is gone or stuck).  Raised on the host;
+    nothing is left running on the GPU by this layer, and the local modules stay usable."""
+
+
+def all_gather_rows(full, local, bounds, group=None, async_op=False):
     """``full[bounds[p]:bounds[p+1]] = rank p's local`` on every rank.  Row counts differ between
     ranks.  NCCL does this as one grouped operation writing straight into ``full``; other
-    backends get one broadcast per rank."""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
+    backends get one broadcast per rank.  ``async_op`` (NCCL only) returns the work handle."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
     lo, hi = int(bounds[rank]), int(bounds[rank + 1])
     if tuple(local.shape[1:]) != tuple(full.shape[1:]) or local.shape[0] != hi - lo:
         raise ValueError("local block has shape %s, rank %d owns rows [%d, %d)" % (tuple(local.shape), rank, lo, hi))
@@ -48,20 +56,20 @@ def all_gather_rows(full, local, bounds, group=None):
         full[lo:hi].copy_(local)
         return full
     views = [full[int(bounds[p]):int(bounds[p + 1])] for p in range(world)]
-    if dist.get_backend(group) == "nccl":
-        dist.all_gather(views, local.contiguous(), group=group)
-    else:
-        views[rank].copy_(local)
-        for p in range(world):
-            if views[p].numel():
-                dist.broadcast(views[p], src=dist.get_global_rank(group, p) if group is not None else p,
-                               group=group)
+    try:
+        if dist.get_backend(group) == "nccl":
+            work = dist.all_gather(views, local.contiguous(), group=group, async_op=async_op)
+            if async_op:
+                return work
+        else:
+            views[rank].copy_(local)
+            for p in range(world):
+                if views[p].numel():
+                    dist.broadcast(views[p], src=dist.get_global_rank(group, p) if group is not None else p,
+                                   group=group)
+    except Exception as exc:  # the process group's timeout, a closed connection, an aborted communicator
+        raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (rank, world, exc)) from exc
     return full
-
-
-class ExchangeError(RuntimeError):
-    """The feature all-gather failed or timed out (a peer rank is gone or stuck).  Raised on the host;
-    nothing is left running on the GPU by this layer, and the local modules stay usable."""
 
 
 def padded_layout(bounds):
@@ -111,6 +119,24 @@ def all_gather_padded(padded, local, bounds, group=None):
     return padded
 
 
+# Padding is worth it while the padded buffer is at most this much larger than the matrix.
+PADDED_LAYOUT_MAX_WASTE = 1.15
+
+
+def use_padded_layout(bounds):
+    """True where equal slots cost little: ``world * largest block <= 1.15 * rows``."""
+    bounds = np.asarray(bounds, dtype=np.int64)
+    world = bounds.shape[0] - 1
+    slot, _ = padded_layout(bounds)
+    return world * slot <= PADDED_LAYOUT_MAX_WASTE * max(int(bounds[-1]), 1)
+
+
+def remap_columns(adj_csr, bounds):
+    """The shard with column ids pointing into the gather buffer of the layout chosen for ``bounds``
+    (unchanged in the plain layout)."""
+    return remap_columns_to_padded(adj_csr, bounds) if use_padded_layout(bounds) else adj_csr
+
+
 class _ShardedBase:
     def __init__(self, bounds, group, device):
         self.group = group
@@ -121,9 +147,28 @@ class _ShardedBase:
         self.row_lo, self.row_hi = int(self.bounds[self.rank]), int(self.bounds[self.rank + 1])
         self.device = device
         self.slot, self.shift = padded_layout(self.bounds)
+        self.padded = use_padded_layout(self.bounds)
+        # rows of the gather buffer every rank holds
+        self.n = self.world * self.slot if self.padded else int(self.bounds[-1])
 
-    def _gather(self, padded, local):
-        return all_gather_padded(padded, local, self.bounds, self.group)
+    def _gather(self, buf, local):
+        if self.padded:
+            return all_gather_padded(buf, local, self.bounds, self.group)
+        return all_gather_rows(buf, local, self.bounds, self.group)
+
+    def _gather_async(self, buf, local):
+        """Start the exchange (NCCL); returns the work handle."""
+        try:
+            if self.padded:
+                rows = self.row_hi - self.row_lo
+                mine = buf[self.rank * self.slot:(self.rank + 1) * self.slot]
+                mine[:rows].copy_(local)
+                return dist.all_gather_into_tensor(buf, mine, group=self.group, async_op=True)
+            return all_gather_rows(buf, local, self.bounds, self.group, async_op=True)
+        except ExchangeError:
+            raise
+        except Exception as exc:
+            raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (self.rank, self.world, exc)) from exc
 
 
 class GatheredFeatures(_ShardedBase):
@@ -135,7 +180,7 @@ class GatheredFeatures(_ShardedBase):
     def __init__(self, bounds, feat_len, group=None, device=None):
         super().__init__(bounds, group, device)
         self.feat_len = int(feat_len)
-        self.full = torch.zeros((self.world * self.slot, self.feat_len), dtype=torch.float32, device=device)
+        self.full = torch.zeros((self.n, self.feat_len), dtype=torch.float32, device=device)
 
     def gather(self, x_local):
         if self.world == 1:
@@ -152,13 +197,7 @@ class GatheredFeatures(_ShardedBase):
         self._work = None
         if self.world == 1 or dist.get_backend(self.group) != "nccl":
             return self.gather(x_local)
-        rows = self.row_hi - self.row_lo
-        mine = self.full[self.rank * self.slot:(self.rank + 1) * self.slot]
-        mine[:rows].copy_(x_local)
-        try:
-            self._work = dist.all_gather_into_tensor(self.full, mine, group=self.group, async_op=True)
-        except Exception as exc:
-            raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (self.rank, self.world, exc)) from exc
+        self._work = self._gather_async(self.full, x_local)
         return self
 
     def wait(self):
@@ -184,10 +223,9 @@ class ShardedSpMM(_ShardedBase):
         super().__init__(bounds, group, device)
         assert local_adj.shape[0] == self.row_hi - self.row_lo
         assert local_adj.shape[1] == int(self.bounds[-1]), "square adjacency expected (features are row-sharded)"
-        # the kernel gathers from the padded all-gather buffer, so its column ids are remapped once
-        self.module = VanillaSpMMcuda(remap_columns_to_padded(local_adj, self.bounds), device=device)
+        # the kernel gathers from the all-gather buffer: in the padded layout the column ids are remapped once
+        self.module = VanillaSpMMcuda(remap_columns(local_adj, self.bounds), device=device)
         self.device = self.module.ctx
-        self.n = self.world * self.slot
         self.x_full = None
 
     def build(self, feat_len, feat_tile=0):
@@ -222,9 +260,8 @@ class ShardedSDDMM(_ShardedBase):
         from .module import VanillaSDDMMcuda
         super().__init__(bounds, group, device)
         assert local_adj.shape[0] == self.row_hi - self.row_lo
-        self.module = VanillaSDDMMcuda(remap_columns_to_padded(local_adj, self.bounds).tocoo(), device=device)
+        self.module = VanillaSDDMMcuda(remap_columns(local_adj, self.bounds).tocoo(), device=device)
         self.device = self.module.ctx
-        self.n = self.world * self.slot
         self.src_full = None
 
     def build(self, feat_len):

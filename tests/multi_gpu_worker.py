@@ -19,13 +19,26 @@ def main():
     device = torch.device("cuda", local_rank)
     dist.init_process_group("nccl", device_id=device)
     world = dist.get_world_size()
+    for graph in ("power-law", "r-mat"):
+        check_graph(graph, rank, world, device)
+    dist.barrier()
+    if rank == 0:
+        print("MULTI_GPU_OK world=%d" % world, flush=True)
+    dist.destroy_process_group()
+
+
+def check_graph(graph, rank, world, device):
     import oracle
     from featgraph_b200 import graphgen
     from featgraph_b200.sharded import GatheredFeatures, ShardedSDDMM, ShardedSpMM, shard_csr_rows
     from featgraph_b200.util import nnz_balanced_row_ranges
 
-    n = 6000
-    adj = graphgen.power_law_graph(n, 600_000, seed=61, kmax=4000)
+    if graph == "power-law":  # row blocks of similar size: the padded gather layout
+        n = 6000
+        adj = graphgen.power_law_graph(n, 600_000, seed=61, kmax=4000)
+    else:  # R-MAT: nnz-balanced blocks of very different row counts: the plain layout, uneven all-gather
+        adj = graphgen.rmat_graph(13, 32, seed=71)
+        n = adj.shape[0]
     bounds = nnz_balanced_row_ranges(adj.indptr, world)
     lo, hi = int(bounds[rank]), int(bounds[rank + 1])
     local = shard_csr_rows(adj, bounds, rank)
@@ -54,10 +67,7 @@ def main():
         np.testing.assert_array_equal(spmm.run(g2.wait()).cpu().numpy(), want)
         want_e = oracle.sddmm(coo.row, coo.col, x, y)[adj.indptr[lo]:adj.indptr[hi]]
         np.testing.assert_allclose(e, want_e, rtol=1e-5, atol=1e-4)
-    dist.barrier()
-    if rank == 0:
-        print("MULTI_GPU_OK world=%d" % world, flush=True)
-    dist.destroy_process_group()
+    assert spmm.padded == (graph == "power-law"), (graph, bounds)
 
 
 if __name__ == "__main__":

@@ -101,6 +101,40 @@ def test_sharding_and_gather_on_cpu_ranks(tmp_path, world):
     assert sorted(os.listdir(tmp_path)) == ["ok%d" % r for r in range(world)]
 
 
+def _worker_layouts(rank, world, port, tmpdir):
+    """GatheredFeatures picks the padded layout for row blocks of similar size and the plain one for
+    very unequal blocks; either way the buffer indexed by the (re)mapped column ids holds x."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import scipy.sparse as sp
+        from featgraph_b200.sharded import GatheredFeatures, remap_columns, shard_csr_rows, use_padded_layout
+        n, d = 300, 8
+        adj = sp.random(n, n, density=0.05, format="csr", random_state=3).astype(np.float32)
+        x = np.random.default_rng(4).random((n, d), dtype=np.float32)
+        for bounds, padded in ((np.array([0, 140, 300]), True), (np.array([0, 10, 300]), False)):
+            assert use_padded_layout(bounds) == padded
+            lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+            g = GatheredFeatures(bounds, d)
+            assert g.padded == padded and g.full.shape[0] == (2 * int(np.diff(bounds).max()) if padded else n)
+            g.gather(torch.from_numpy(x[lo:hi].copy()))
+            local = remap_columns(shard_csr_rows(adj, bounds, rank), bounds)
+            assert local.shape == (hi - lo, g.full.shape[0])
+            np.testing.assert_array_equal(g.full.numpy()[local.indices], x[adj.indices[adj.indptr[lo]:adj.indptr[hi]]])
+            g.gather_async(torch.from_numpy(x[lo:hi].copy())).wait()  # gloo: the blocking path
+            np.testing.assert_array_equal(g.full.numpy()[local.indices], x[adj.indices[adj.indptr[lo]:adj.indptr[hi]]])
+        open(os.path.join(tmpdir, "ok%d" % rank), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_layout_follows_the_row_ranges(tmp_path):
+    mp.spawn(_worker_layouts, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
 def _worker_peer_leaves(rank, world, port, tmpdir):
     """Rank 1 leaves between steps (no collective in flight); rank 0's next exchange must end with an
     ExchangeError within the process group's timeout instead of hanging."""
