@@ -98,7 +98,9 @@ void fg_row_schedule_destroy(fg_row_schedule* schedule);
  *              shared-memory ring; heavy rows: one block per row and tile, its warps taking
  *              turns).  When no 32-float slice of x can stay in L2 those kernels run on an
  *              internal second stream beside the main one, forked from and joined to `stream`
- *              by events (legal under stream capture).  No effect on the values.
+ *              by events (legal under stream capture; the streams and events are created on a
+ *              host thread's first such call per device, so make that call outside a capture).
+ *              No effect on the values.
  *   feat_tile  width in floats of the feature slice handled per pass over the rows
  *              (power of two, 4..128), 0 = choose from n_cols and the L2 size.  It is the
  *              reference's num_feat_partitions idea (op/vanilla_spmm.py:41-44) used to keep
