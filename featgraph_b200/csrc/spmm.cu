@@ -21,11 +21,11 @@
 // similar-length) rows, so the warp-uniform loop below wastes few iterations.
 //
 // Long rows.  A row cannot be split between workers (its sum is sequential), so the time of
-// the longest row is a floor under the whole launch: with 8 gathers in flight a 20,000-nonzero
-// row costs 2,500 dependent round trips to L2.  Rows the launch counts as long therefore go to
+// the longest row is a floor under the whole launch: with 16 gathers in flight a 20,000-nonzero
+// row costs 1,250 dependent round trips to L2.  Rows the launch counts as long therefore go to
 // spmm_long_rows_kernel, which stages feature slices through a shared-memory ring filled by
 // cp.async (64 nonzeros in flight per row; the same sums, a deeper pipeline, 15 ns per nonzero of
-// a row instead of 75), and the very longest to spmm_heavy_rows_kernel, where the warps of a block
+// a row instead of 40), and the very longest to spmm_heavy_rows_kernel, where the warps of a block
 // share one row's ring and take turns at its sum (7 ns per nonzero).  They are launched first; the
 // remaining rows follow in spmm_rows_kernel.
 #include <cmath>
@@ -97,11 +97,15 @@ struct Slice<1> {
 
 // G lanes per (row, tile) unit; VEC floats per lane; DDS selects the two-level sum; UNIT: every
 // adjacency value is 1.0 (no value array is read, and 1.0 * x == x exactly, so nothing is multiplied).
+// The regular form keeps 16 gathers (16 x 128 bits per lane) in flight per row with 2 blocks per SM:
+// the same bytes in flight per SM as 8 gathers with 4 blocks, but a row advances twice as fast
+// (about 40 instead of 75 ns per nonzero), which is what bounds a launch on a shard, and the
+// throughput measured slightly higher as well (233K-node graph, d = 64: 1.60 -> 1.42 ms).
 // SHORT: the form for rows of a few nonzeros, where what counts is how many rows an SM has in
-// flight, not how many gathers a row has: 4 gathers back to back and 6 blocks per SM instead of 8 and 4.
+// flight, not how many gathers a row has: 4 gathers back to back and 6 blocks per SM.
 template <int G, int VEC, bool DDS, bool UNIT, bool SHORT>
-__global__ void __launch_bounds__(kThreads, SHORT ? 6 : 4) spmm_rows_kernel(const SpmmArgs a) {
-    constexpr int CHMAX = SHORT ? 4 : 8;
+__global__ void __launch_bounds__(kThreads, SHORT ? 6 : 2) spmm_rows_kernel(const SpmmArgs a) {
+    constexpr int CHMAX = SHORT ? 4 : 16;
     constexpr int CH = G < CHMAX ? G : CHMAX;  // gathers issued back to back
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
@@ -531,8 +535,9 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
 // Which rows (from the front of the schedule) go to the heavy-row and long-row kernels for this launch.
 //
 // The three kernels trade throughput against the time of one row.  Measured on B200 (C2 graph):
-//   spmm_rows_kernel       streams gathers at about 17 TB/s, about 75 ns per nonzero of one row
-//                          (8 gathers per L2 round trip): a 20,000-nonzero row alone takes 1.5 ms;
+//   spmm_rows_kernel       streams gathers at about 19 TB/s, about 40 ns per nonzero of one row
+//                          (16 gathers per L2 round trip; 75 ns with tiles of 32 floats, where a row
+//                          has 8 lanes and 8 gathers): a 20,000-nonzero row alone takes 0.8 ms;
 //   spmm_long_rows_kernel  about 13 TB/s (every slice crosses shared memory twice), 15 ns per nonzero;
 //   spmm_heavy_rows_kernel with 4 warps per block about 9 TB/s and 7 ns per nonzero, with 8 warps
 //                          about 6 TB/s and 5 ns (more time for a warp to refill between turns).
@@ -545,7 +550,11 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
 // part stretched to that sum.  Every pair of candidate thresholds is tried and the
 // cheapest wins.  A threshold fixed at schedule creation overrides the choice.  The choice never
 // affects a result bit.
-constexpr double kRowsRate = 17e12, kRowsSecPerNnz = 75e-9;
+constexpr double kRowsRate = 19e12;
+// per nonzero of one row: about 40 ns measured with 16 gathers in flight, 75 with 8 (tiles of 32 floats: 8
+// lanes per row); the model uses a cautious 55 for the former - too low a figure leaves long rows in this
+// kernel, and their time is then added to the whole launch
+constexpr double kRowsSecPerNnz16 = 55e-9, kRowsSecPerNnz8 = 75e-9;
 constexpr double kRingRate = 13e12, kRingSecPerNnz = 15e-9;
 constexpr double kHeavyRate[2] = {9e12, 6e12}, kHeavySecPerNnz[2] = {7.5e-9, 5e-9};  // 4 / 8 warps
 
@@ -591,7 +600,7 @@ RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, boo
         const double s_rows = nnz_rows * short_bytes / kRowsRate;
         const double heavy_row = longest * kHeavySecPerNnz[wide];
         const double ring_row = fmin(t_heavy, longest) * kRingSecPerNnz;
-        const double rows_row = fmin(t_ring, longest) * kRowsSecPerNnz;
+        const double rows_row = fmin(t_ring, longest) * (short_tile >= 64 ? kRowsSecPerNnz16 : kRowsSecPerNnz8);
         if (!side_by_side)
             return part(s_heavy, long_tiles, heavy_row) + part(s_ring, long_tiles, ring_row) +
                    part(s_rows, short_tiles, rows_row);
