@@ -565,7 +565,7 @@ def run_ours(args):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; keyed by (op, feature length).  Absent = not captured.
 NCU_TRAFFIC_BYTES = {
-    ("spmm", 512): 12.17e9,   # spmm_rows_kernel<16,4,0,1>, one launch (8 tiles inside)
+    ("spmm", 512): 10.6e9,    # spmm_rows_kernel<16,4,0,1,0>, one launch (8 tiles inside)
     ("spmm", 128): 3.22e9,
     ("sddmm", 512): 25.7e9,   # sddmm_tile_kernel<8,2,4,1,0>: 8 tile launches of 3.21 GB each
     ("sddmm", 128): 7.58e9,   # two tile launches
