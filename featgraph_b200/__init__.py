@@ -20,6 +20,10 @@ def host_sync(device=None):
     import ctypes
     import torch
     from . import _native
+    from .module import _device
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
     with torch.cuda.device(dev):
         _native.check(_native.lib().fg_host_sync(ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    _device.note_host_sync(dev)  # modules with a deferred call pending on this device are usable again

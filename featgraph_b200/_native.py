@@ -52,12 +52,27 @@ def library_path():
 
 
 def lib():
-    """Load (building first if the sources are newer) and return the ctypes library."""
+    """Load and return the ctypes library.  Where nvcc is present the library is first brought up
+    to date with its sources (``build.build_cuda()`` compiles only what is older than a source or
+    header and does nothing otherwise), so an edited kernel can never be tested against a stale
+    binary.  Without nvcc an existing library is loaded as it is; with neither, this raises.
+    ``FEATGRAPH_B200_LIB=/path/to/lib.so`` loads that file instead, without building."""
     global _lib
     if _lib is None:
         path = _build.CUDA_LIB
-        if not os.path.exists(path) or os.environ.get("FEATGRAPH_B200_REBUILD"):
-            path = _build.build_cuda()
+        override = os.environ.get("FEATGRAPH_B200_LIB")  # a prebuilt library to load as it is
+        try:
+            _build._nvcc()
+            have_nvcc = True
+        except RuntimeError:
+            have_nvcc = False
+        if override:
+            path = override
+        elif have_nvcc:
+            path = _build.build_cuda(force=bool(os.environ.get("FEATGRAPH_B200_REBUILD")))
+        elif not os.path.exists(path):
+            raise RuntimeError("featgraph_b200: %s is missing and nvcc is not available to build it "
+                               "(there is no CPU fallback)" % path)
         L = ctypes.CDLL(path)
         for name, (res, args) in SIGNATURES.items():
             f = getattr(L, name)  # AttributeError here = header and library out of step

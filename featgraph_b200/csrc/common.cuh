@@ -25,6 +25,17 @@ int fail(int code, const char* fmt, ...);
 // Kernels launched by this library in this process (fg_kernel_launch_count).
 void count_launches(int n);
 
+// SM count and L2 size of the current device, looked up once per device ordinal (a host thread may
+// move between devices; each device keeps its own figures).
+constexpr int kMaxDevices = 64;
+struct DeviceProps {
+    int sm_count = 148;
+    int64_t l2_bytes = 64ll << 20;
+};
+DeviceProps device_props();
+// Ordinal of the current device, or -1 if it cannot be had or is beyond kMaxDevices.
+int current_device_slot();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int pow2_floor(int v) {

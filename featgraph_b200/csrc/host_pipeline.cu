@@ -18,21 +18,11 @@
 namespace {
 
 struct Pipeline {
-    int device = -1;
     cudaStream_t in = nullptr, out = nullptr;
     std::vector<cudaEvent_t> events;
     size_t next = 0;
 
     int prepare() {
-        int dev = 0;
-        FG_CUDA_TRY(cudaGetDevice(&dev));
-        if (dev != device) {
-            // a thread that moves to another device gets fresh objects there; the old ones are
-            // few and are left to the context
-            in = out = nullptr;
-            events.clear();
-            device = dev;
-        }
         if (!in) FG_CUDA_TRY(cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking));
         if (!out) FG_CUDA_TRY(cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking));
         // events are handed out round robin; 512 in rotation is far more than the calls that can be
@@ -51,9 +41,12 @@ struct Pipeline {
     }
 };
 
-Pipeline& pipeline() {
-    static thread_local Pipeline p;
-    return p;
+// One pipeline per host thread and device: a thread that alternates between devices finds its streams
+// and events again when it returns to a device.
+Pipeline* pipeline() {
+    static thread_local Pipeline table[fg::kMaxDevices];
+    const int dev = fg::current_device_slot();
+    return dev < 0 ? nullptr : &table[dev];
 }
 
 // columns [c0, c0 + w) of a row-major [rows, d] matrix, host <-> device
@@ -94,14 +87,19 @@ int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indpt
     if (!h_out || !d_out_staging || (n_cols > 0 && (!h_x || !d_x_staging)))
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL host or staging buffer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    Pipeline& p = pipeline();
+    Pipeline* pp = pipeline();
+    if (!pp) return fg::fail(FG_ERR_CUDA, "no current CUDA device (or its ordinal is beyond %d)", fg::kMaxDevices);
+    Pipeline& p = *pp;
     FG_TRY_RC(p.prepare());
     const int w = window_width(d, chunk);
     const bool deferred = (flags & FG_HOST_DEFERRED) != 0;
     if (!deferred) {
+        // the staging buffers may still be in use by earlier work on the caller's stream.  A deferred
+        // call does not wait (its copy-in is meant to run beside the previous call's kernels); there the
+        // caller keeps the staging buffers of calls in flight apart, as the header says.
         cudaEvent_t start;
         FG_TRY_RC(p.event(&start));
-        FG_CUDA_TRY(cudaEventRecord(start, s));  // staging buffers may still be in use on the caller's stream
+        FG_CUDA_TRY(cudaEventRecord(start, s));
         FG_CUDA_TRY(cudaStreamWaitEvent(p.in, start, 0));
         FG_CUDA_TRY(cudaStreamWaitEvent(p.out, start, 0));
     }
@@ -137,11 +135,13 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
     if (!h_src || !h_dst || !h_out || !d_src_staging || !d_dst_staging || !d_out_staging)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL host or staging buffer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    Pipeline& p = pipeline();
+    Pipeline* pp = pipeline();
+    if (!pp) return fg::fail(FG_ERR_CUDA, "no current CUDA device (or its ordinal is beyond %d)", fg::kMaxDevices);
+    Pipeline& p = *pp;
     FG_TRY_RC(p.prepare());
     const int w = window_width(d, chunk);
     const bool deferred = (flags & FG_HOST_DEFERRED) != 0;
-    if (!deferred) {
+    if (!deferred) {  // as above
         cudaEvent_t start;
         FG_TRY_RC(p.event(&start));
         FG_CUDA_TRY(cudaEventRecord(start, s));
@@ -171,10 +171,10 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
 }
 
 int fg_host_sync(void* stream) {
-    Pipeline& p = pipeline();
-    if (p.in) FG_CUDA_TRY(cudaStreamSynchronize(p.in));
+    Pipeline* p = pipeline();
+    if (p && p->in) FG_CUDA_TRY(cudaStreamSynchronize(p->in));
     FG_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-    if (p.out) FG_CUDA_TRY(cudaStreamSynchronize(p.out));
+    if (p && p->out) FG_CUDA_TRY(cudaStreamSynchronize(p->out));
     return FG_OK;
 }
 

@@ -1,5 +1,6 @@
 // Error text, version and device query of the C ABI.
 #include <atomic>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -22,6 +23,34 @@ namespace {
 std::atomic<long long> g_launches{0};
 }
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int current_device_slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -1;
+    }
+    return (dev >= 0 && dev < kMaxDevices) ? dev : -1;
+}
+
+DeviceProps device_props() {
+    static std::mutex lock;
+    static DeviceProps table[kMaxDevices];
+    static bool known[kMaxDevices] = {false};
+    const int dev = current_device_slot();
+    if (dev < 0) return DeviceProps();
+    std::lock_guard<std::mutex> hold(lock);
+    if (!known[dev]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+            table[dev].sm_count = v;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) == cudaSuccess && v > 0)
+            table[dev].l2_bytes = v;
+        (void)cudaGetLastError();
+        known[dev] = true;
+    }
+    return table[dev];
+}
 
 }  // namespace fg
 

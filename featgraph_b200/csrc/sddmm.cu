@@ -359,18 +359,7 @@ int launch_width(const SddmmArgs& a, bool cache, unsigned blocks, cudaStream_t s
 #undef FG_SDDMM
 }
 
-int64_t l2_size_bytes() {
-    static thread_local int64_t l2 = -1;
-    if (l2 < 0) {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) == cudaSuccess)
-            l2 = v;
-        else
-            l2 = 64ll << 20;
-    }
-    return l2;
-}
+int64_t l2_size_bytes() { return fg::device_props().l2_bytes; }
 
 }  // namespace
 

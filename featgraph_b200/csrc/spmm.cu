@@ -14,7 +14,7 @@
 // contiguous bytes per nonzero (one or more full 128-byte lines for G >= 8).  Column
 // indices (and values, unless the adjacency is unweighted) are fetched G at a time,
 // coalesced, one batch ahead of use, and passed to the group's lanes with shuffles; the
-// gathers of up to 8 nonzeros are issued before the first of them is consumed.
+// gathers of up to 16 nonzeros are issued before the first of them is consumed.
 //
 // Balance.  Rows are visited in the order of an fg_row_schedule (heaviest first), blocks
 // are launched in that order, and the groups sharing a warp hold neighbouring (hence
@@ -558,18 +558,7 @@ constexpr double kRowsSecPerNnz16 = 55e-9, kRowsSecPerNnz8 = 75e-9;
 constexpr double kRingRate = 13e12, kRingSecPerNnz = 15e-9;
 constexpr double kHeavyRate[2] = {9e12, 6e12}, kHeavySecPerNnz[2] = {7.5e-9, 5e-9};  // 4 / 8 warps
 
-int sm_count() {
-    static thread_local int n = 0;
-    if (n == 0) {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
-            n = v;
-        else
-            n = 148;
-    }
-    return n;
-}
+int sm_count() { return fg::device_props().sm_count; }
 
 struct RowSplit {
     int64_t heavy = 0;  // order[0, heavy): spmm_heavy_rows_kernel
@@ -645,31 +634,22 @@ RowSplit choose_row_split(const fg_row_schedule& sch, int d, int short_tile, boo
 // the caller's stream sees one call that is complete when all kernels are, also under stream capture.
 struct SideStream {
     enum { kHeavy = 0, kRing = 1, kShort = 2, kStreams = 3 };
-    int device = -1;
     cudaStream_t stream[kStreams] = {nullptr, nullptr, nullptr};
     cudaEvent_t fork = nullptr, join[kStreams] = {nullptr, nullptr, nullptr};
     bool prepare() {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return false;
-        if (dev != device) {  // a thread that moves to another device gets fresh objects there
-            for (int i = 0; i < kStreams; ++i) stream[i] = nullptr, join[i] = nullptr;
+        if (fork) return true;
+        int least = 0, greatest = 0;
+        cudaDeviceGetStreamPriorityRange(&least, &greatest);
+        bool ok = cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < kStreams; ++i)
+            // the heaviest rows bound the launch: their blocks go first
+            ok = cudaStreamCreateWithPriority(&stream[i], cudaStreamNonBlocking,
+                                              i == kShort ? least : greatest) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&join[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {
+            (void)cudaGetLastError();
             fork = nullptr;
-            device = dev;
-        }
-        if (!fork) {
-            int least = 0, greatest = 0;
-            cudaDeviceGetStreamPriorityRange(&least, &greatest);
-            bool ok = cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) == cudaSuccess;
-            for (int i = 0; ok && i < kStreams; ++i)
-                // the heaviest rows bound the launch: their blocks go first
-                ok = cudaStreamCreateWithPriority(&stream[i], cudaStreamNonBlocking,
-                                                  i == kShort ? least : greatest) == cudaSuccess &&
-                     cudaEventCreateWithFlags(&join[i], cudaEventDisableTiming) == cudaSuccess;
-            if (!ok) {
-                (void)cudaGetLastError();
-                fork = nullptr;
-                return false;
-            }
+            return false;
         }
         return true;
     }
@@ -690,9 +670,12 @@ struct SideStream {
     }
 };
 
-SideStream& side_stream() {
-    static thread_local SideStream s;
-    return s;
+// One set per host thread and device: a thread that alternates between devices (one process driving
+// several GPUs) finds its objects again when it returns to a device.  nullptr: no usable device slot.
+SideStream* side_stream() {
+    static thread_local SideStream table[fg::kMaxDevices];
+    const int dev = fg::current_device_slot();
+    return dev < 0 ? nullptr : &table[dev];
 }
 
 int launch_long(const SpmmArgs& a, cudaStream_t s) {
@@ -774,16 +757,7 @@ int launch_tile(const SpmmArgs& a, int tile, bool dds, cudaStream_t s) {
 
 // The share of L2 in which a gathered slice of x stays resident under all-SM random access.
 int64_t l2_budget() {
-    static thread_local int64_t l2_bytes = -1;
-    if (l2_bytes < 0) {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) == cudaSuccess)
-            l2_bytes = v;
-        else
-            l2_bytes = 64ll << 20;
-    }
-    return l2_bytes / 2;  // each half of the chip caches its own copy
+    return fg::device_props().l2_bytes / 2;  // each half of the chip caches its own copy
 }
 
 // Can a 32-float slice of x (the narrowest tile that gathers whole 128-byte lines) stay in L2?
@@ -828,6 +802,13 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     if (schedule && fg_row_schedule_num_rows(schedule) != n_rows)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "row schedule was built for %lld rows, not %lld",
                         (long long)fg_row_schedule_num_rows(schedule), (long long)n_rows);
+    // The rows kernels read each row's extent from the schedule's cache, not from the position array
+    // of this call: a schedule built from another adjacency would send gathers out of bounds.
+    if (schedule && !dds && schedule->d_extent && schedule->nnz != nnz)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT,
+                        "row schedule was built from an adjacency of %lld nonzeros, this call has %lld: "
+                        "rebuild the schedule when the adjacency changes",
+                        (long long)schedule->nnz, (long long)nnz);
 
     SpmmArgs a;
     a.pos = pos;
@@ -875,9 +856,9 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
         first_short = schedule->rows_at_least[0];
         if (first_short < split.ring) first_short = split.ring;
     }
-    SideStream& side = side_stream();
-    const bool forked = side_by_side && (split.ring > 0 || first_short < n_rows) && side.fork_from(s);
-    auto stream_for = [&](int which) { return forked ? side.stream[which] : s; };
+    SideStream* side = side_stream();
+    const bool forked = side && side_by_side && (split.ring > 0 || first_short < n_rows) && side->fork_from(s);
+    auto stream_for = [&](int which) { return forked ? side->stream[which] : s; };
     int rc = FG_OK;
     {
         SpmmArgs h = a;
@@ -905,7 +886,7 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     // join even after a failed launch: the side streams must come back to the caller's stream (a
     // capture could not end otherwise); work enqueued on it afterwards waits for all kernels
     if (forked) {
-        const int rcj = side.join_to(s);
+        const int rcj = side->join_to(s);
         if (rc == FG_OK) rc = rcj;
     }
     return rc;
@@ -1046,6 +1027,7 @@ int fg_spmm_csr_f32_static(const int32_t* d_indptr, const int32_t* d_indices, co
     fg_row_schedule view;
     view.d_order = order;
     view.n_rows = n_rows;
+    view.nnz = nnz;
     view.fixed_threshold = INT32_MAX;
     view.fixed_rows = 0;
     view.rows_at_least[0] = n_rows;  // no degree statistics here: one kernel form for all rows, no side streams

@@ -86,5 +86,27 @@ def time_calls(fn, device, num_runs):
         return start.elapsed_time(stop) * 1e-3 / num_runs
 
 
+# Deferred host-buffer calls (run_host(wait=False)) leave a module's staging buffers in use until the
+# next host_sync() on that device; a module that is called again before that would overwrite them
+# under a kernel that still reads them.  Each host_sync() starts a new epoch per device; a module
+# remembers the epoch of its pending deferred call and refuses further calls within it.
+_sync_epoch = {}
+
+
+def sync_epoch(device):
+    return _sync_epoch.get(device.index, 0)
+
+
+def note_host_sync(device):
+    _sync_epoch[device.index] = _sync_epoch.get(device.index, 0) + 1
+
+
+def refuse_if_deferred_pending(module):
+    if getattr(module, "_deferred_epoch", None) == sync_epoch(module._device):
+        raise RuntimeError("this module has a deferred run_host(wait=False) call in flight: call "
+                           "featgraph_b200.host_sync() before using the module again (its staging "
+                           "buffers are still being read)")
+
+
 lib = _native.lib
 check = _native.check

@@ -141,6 +141,7 @@ class SDDMMbase:
         same object every call, reference :115-129).  Argument order: [column-side, row-side]."""
         if self.out is None:
             raise RuntimeError("call build() before run()")
+        dev.refuse_if_deferred_pending(self)
         src, dst = inputs
         dev.check_input(src, self._shapes[0], self._device, "column-side features")
         dev.check_input(dst, self._shapes[1], self._device, "row-side features")
@@ -153,9 +154,10 @@ class SDDMMbase:
         contiguous; pinned for full copy speed), per-edge result back in host memory, copies
         pipelined against the kernels by ``fg_sddmm_coo_f32_host``.  Returns the host tensor.
         ``wait=False``: return at once; the tensor is complete after ``featgraph_b200.host_sync()``
-        (lets this call's copy-out overlap the next call; do not reuse this module before that)."""
+        (lets this call's copy-out overlap the next call; using this module again before that raises)."""
         if self.out is None:
             raise RuntimeError("call build() before run_host()")
+        dev.refuse_if_deferred_pending(self)
         ts = [torch.from_numpy(x) if isinstance(x, np.ndarray) else x for x in inputs]
         for t, shape in zip(ts, self._shapes):
             if t.device.type != "cpu" or t.dtype != torch.float32 or not t.is_contiguous() \
@@ -176,6 +178,8 @@ class SDDMMbase:
                 ctypes.c_void_p(ts[1].data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(self._staging[0]),
                 dev.ptr(self._staging[1]), dev.ptr(self.out), self._num_rows, self._num_cols, self._nnz, d,
                 self._rows_sorted, int(chunk), 0 if wait else 1, dev.stream_ptr(self._device)))
+            if not wait:
+                self._deferred_epoch = dev.sync_epoch(self._device)
         return out
 
     def measure_average_time(self, inputs, num_runs):

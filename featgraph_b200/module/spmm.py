@@ -153,6 +153,7 @@ class SpMMbase:
         (the same object every call, as the reference returns ``out_tvm``, :142-161)."""
         if self.out is None:
             raise RuntimeError("call build() before run()")
+        dev.refuse_if_deferred_pending(self)
         (x,) = inputs
         dev.check_input(x, self._feat_shape, self._device, "source features")
         with torch.cuda.device(self._device):
@@ -165,9 +166,10 @@ class SpMMbase:
         kernels are pipelined over column windows by ``fg_spmm_csr_f32_host``.  ``out``: a CPU
         float32 tensor ``[num_rows, feat_len]`` to fill (allocated pinned if omitted).  Returns it.
         ``wait=False``: return at once; the tensor is complete after ``featgraph_b200.host_sync()``
-        (lets this call's copy-out overlap the next call; do not reuse this module before that)."""
+        (lets this call's copy-out overlap the next call; using this module again before that raises)."""
         if self.out is None:
             raise RuntimeError("call build() before run_host()")
+        dev.refuse_if_deferred_pending(self)
         (x,) = inputs
         xt = torch.from_numpy(x) if isinstance(x, np.ndarray) else x
         if xt.device.type != "cpu" or xt.dtype != torch.float32 or not xt.is_contiguous() \
@@ -191,6 +193,8 @@ class SpMMbase:
                 ctypes.c_void_p(xt.data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(self._x_staging),
                 dev.ptr(self.out), self._num_rows, self._num_cols, self._nnz, d, int(chunk),
                 0 if wait else 1, dev.stream_ptr(self._device)))
+            if not wait:
+                self._deferred_epoch = dev.sync_epoch(self._device)
         return out
 
     def measure_average_time(self, inputs, num_runs):

@@ -63,8 +63,12 @@ int fg_device_info(int32_t* sm_count, int32_t* cc_major, int32_t* cc_minor, int6
  * Row schedule: the order in which SpMM visits rows (heaviest rows first, ties in
  * row order).  It takes the place of the reference's launch-shape knobs
  * num_cuda_blocks / num_threads_per_cuda_block (python/featgraph/op/vanilla_spmm.py:128-146),
- * which only choose how rows map to blocks.  Built once per adjacency on the device;
- * holds n_rows int32 of device memory.  Results never depend on it.
+ * which only choose how rows map to blocks.  Built once per adjacency on the device; holds
+ * 12 bytes of device memory per row: the row ids in visiting order and, beside each, a copy of
+ * that row's (first nonzero, count) taken from d_indptr.  The kernels read those copies instead of
+ * the position array of the call, so a schedule belongs to the exact d_indptr it was built from:
+ * rebuild it when the adjacency changes.  A call whose nnz differs from the schedule's is refused
+ * (FG_ERR_INVALID_ARGUMENT).  With the matching adjacency the schedule never changes a result bit.
  * -------------------------------------------------------------------------------------- */
 typedef struct fg_row_schedule fg_row_schedule;
 
@@ -100,7 +104,7 @@ void fg_row_schedule_destroy(fg_row_schedule* schedule);
  *              internal second stream beside the main one, forked from and joined to `stream`
  *              by events (legal under stream capture; the streams and events are created on a
  *              host thread's first such call per device, so make that call outside a capture).
- *              No effect on the values.
+ *              No effect on the values, provided the schedule was built from this d_indptr.
  *   feat_tile  width in floats of the feature slice handled per pass over the rows
  *              (power of two, 4..128), 0 = choose from n_cols and the L2 size.  It is the
  *              reference's num_feat_partitions idea (op/vanilla_spmm.py:41-44) used to keep

@@ -117,3 +117,32 @@ def test_graph_generators_are_deterministic_and_well_formed():
     x = g.uniform_features((64, 8), seed=5)
     assert x.dtype == np.float32 and x.min() >= -1.0 and x.max() < 1.0
     assert np.array_equal(x, g.uniform_features((64, 8), seed=5))
+
+
+def test_loading_the_library_rebuilds_it_when_a_source_is_newer(monkeypatch):
+    """An edited kernel must never be tested against a stale binary: lib() asks build_cuda() to bring the
+    library up to date, and build_cuda() compiles exactly when a source or header is newer than the .so."""
+    import time
+    from featgraph_b200 import _native, build
+    build.build_cuda()
+    assert not build.cuda_stale()
+    src = os.path.join(build.CSRC, "validate.cu")
+    st = os.stat(src)
+    try:
+        os.utime(src, (time.time() + 60, time.time() + 60))
+        assert build.cuda_stale()
+        # what lib() does on first use: it must reach the compiler for a stale library
+        asked = []
+        monkeypatch.setattr(build, "build_cuda", lambda force=False, **kw: asked.append(force) or build.CUDA_LIB)
+        monkeypatch.setattr(_native, "_lib", None)
+        _native.lib()
+        assert asked == [False]
+    finally:
+        os.utime(src, (st.st_atime, st.st_mtime))
+    assert not build.cuda_stale()
+    # a library named by FEATGRAPH_B200_LIB is loaded as it is, without a build
+    asked.clear()
+    monkeypatch.setenv("FEATGRAPH_B200_LIB", build.CUDA_LIB)
+    monkeypatch.setattr(_native, "_lib", None)
+    _native.lib()
+    assert asked == []

@@ -101,9 +101,16 @@ def test_host_buffer_calls_pipeline_windows_and_match_device_calls(oracle, d, ch
     xp, yp = torch.from_numpy(x).pin_memory(), torch.from_numpy(y).pin_memory()
     sp_.run_host([xp], out=o1, chunk=chunk, wait=False)
     sd.run_host([xp, yp], out=o2, chunk=chunk, wait=False)
+    # a module with a deferred call in flight refuses further calls (its staging buffers are in use)
+    with pytest.raises(RuntimeError, match="deferred"):
+        sp_.run_host([xp], out=o1, chunk=chunk, wait=False)
+    with pytest.raises(RuntimeError, match="deferred"):
+        sd.run([torch.from_numpy(x).cuda(), torch.from_numpy(y).cuda()])
     featgraph_b200.host_sync()
     np.testing.assert_array_equal(o1.numpy(), want)
     np.testing.assert_allclose(o2.numpy(), oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)
+    # ... and is usable again after host_sync()
+    np.testing.assert_array_equal(sp_.run_host([xp], out=o1, chunk=chunk).numpy(), want)
 
 
 def test_spmm_build_and_run_argument_errors(adj_csr):

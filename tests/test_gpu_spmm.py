@@ -255,3 +255,24 @@ def test_bad_adjacency_is_reported():
     good = G.dev(np.array([0, 1, 2, 3], np.int32))
     assert L.fg_csr_validate(G.p(good), G.p(indices), 3, 4, 3, G.stream()) == 4  # column 9 of 4
     assert L.fg_csr_validate(G.p(good), G.p(indices), 3, 10, 3, G.stream()) == 0
+
+
+def test_schedule_of_another_adjacency_is_refused():
+    """The rows kernels take row extents from the schedule's cache: a schedule built from a different
+    adjacency (same row count, other nonzero count) must be refused on the host, not run."""
+    import torch
+    import gpu_util as G
+    from featgraph_b200 import _native, graphgen
+    a = graphgen.fixed_degree_graph(300, 20, seed=5)
+    b = graphgen.fixed_degree_graph(300, 12, seed=6)
+    x = G.dev(graphgen.uniform_features((300, 16), seed=7))
+    ip_a, ip_b, ix_b = G.dev(a.indptr, np.int32), G.dev(b.indptr, np.int32), G.dev(b.indices, np.int32)
+    sch = G.Schedule(ip_a, 300)
+    out = torch.zeros(300 * 16, device="cuda")
+    L = _native.lib()
+    rc = L.fg_spmm_csr_f32(sch.h, G.p(ip_b), G.p(ix_b), None, G.p(x), 0, G.p(out), 0, 300, 300, b.nnz, 16, 0,
+                           G.stream())
+    assert rc == 1 and b"rebuild the schedule" in L.fg_last_error()
+    torch.cuda.synchronize()
+    assert not out.any()  # nothing ran
+    sch.close()
