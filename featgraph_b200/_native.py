@@ -28,6 +28,12 @@ SIGNATURES = {
     "fg_spmm_csr_f32_static": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fg_spmm_dds_f32": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "fg_sddmm_coo_f32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "fg_sddmm_auto_partitions": (_i32, [_i64, _i64, _i64, _i32]),
+    "fg_sddmm_plan_create": (ctypes.c_int, [_vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "fg_sddmm_plan_partitions": (_i32, [_vp]),
+    "fg_sddmm_plan_batches": (_i64, [_vp]),
+    "fg_sddmm_plan_destroy": (None, [_vp]),
+    "fg_sddmm_coo_f32_planned": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fg_sddmm_coo_f32_exact": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fg_spmm_csr_f32_host": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "fg_sddmm_coo_f32_host": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp]),

@@ -96,8 +96,12 @@ def build_cuda(force=False, verbose=False, extra=(), target=None):
     variant = bool(extra) or target is not None
     if not (force or variant or _newer(out, srcs + hdrs)):
         return out
-    objdir = os.path.join(LIBDIR, "obj" if not variant else "obj_" + os.path.basename(out))
-    os.makedirs(objdir, exist_ok=True)
+    if variant:  # objects of a variant build are of no further use
+        import tempfile
+        objdir = tempfile.mkdtemp(prefix="fg_obj_")
+    else:
+        objdir = os.path.join(LIBDIR, "obj")
+        os.makedirs(objdir, exist_ok=True)
     lock = _locked(os.path.join(LIBDIR, ".build.lock"))
     try:
         if not (force or variant or _newer(out, srcs + hdrs)):
@@ -138,6 +142,8 @@ def build_cuda(force=False, verbose=False, extra=(), target=None):
         os.replace(tmp, out)  # a process that has the old file mapped keeps it; new loads see the new one
     finally:
         lock.close()
+        if variant:
+            shutil.rmtree(objdir, ignore_errors=True)
     return out
 
 

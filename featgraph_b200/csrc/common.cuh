@@ -54,6 +54,52 @@ __device__ __forceinline__ float4 ldg4(const float* p) {
     return __ldg(reinterpret_cast<const float4*>(p));
 }
 
+// L2 residency hints.  The kernels gather from a slice of the feature matrix that is sized to stay in
+// L2 while index arrays and outputs stream past it once per pass; without a hint the streams push
+// slice lines out.  Gathers therefore ask L2 to evict their lines last, streams to evict theirs first.
+#ifndef FG_HINT_KEEP
+#define FG_HINT_KEEP 0
+#endif
+#ifndef FG_HINT_STREAM
+#define FG_HINT_STREAM 0
+#endif
+__device__ __forceinline__ uint64_t l2_keep_policy() {
+    uint64_t p = 0;
+#if FG_HINT_KEEP
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+#endif
+    return p;
+}
+// gather with the evict-last policy
+__device__ __forceinline__ float4 ldg4_keep(const float* p, uint64_t policy) {
+#if FG_HINT_KEEP
+    float4 v;
+    asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+        : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+        : "l"(p), "l"(policy));
+    return v;
+#else
+    return ldg4(p);
+#endif
+}
+// streamed (read-once / write-once) data: evict first
+template <typename T>
+__device__ __forceinline__ T ld_stream(const T* p) {
+#if FG_HINT_STREAM
+    return __ldcs(p);
+#else
+    return *p;
+#endif
+}
+template <typename T>
+__device__ __forceinline__ void st_stream(T* p, T v) {
+#if FG_HINT_STREAM
+    __stcs(p, v);
+#else
+    *p = v;
+#endif
+}
+
 // acc + a*b with two roundings (never contracted into an FMA).
 __device__ __forceinline__ float mul_then_add(float acc, float a, float b) {
     return __fadd_rn(acc, __fmul_rn(a, b));

@@ -33,6 +33,10 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kBatchesPerWarp = 16;  // 16 x 32 consecutive edges per warp
+#ifndef FG_SDDMM_UNROLL
+#define FG_SDDMM_UNROLL 1
+#endif
+constexpr int kBatchUnroll = FG_SDDMM_UNROLL;
 
 __device__ __forceinline__ float dot4(float acc, const float4& a, const float4& b) {
     acc = fmaf(a.x, b.x, acc);
@@ -55,11 +59,13 @@ struct SddmmArgs {
     int32_t accumulate;
 };
 
-// G lanes per edge, NV float4 per lane, U edges' gathers in flight per group.
+// G lanes per edge, NV float4 per lane, U edges' gathers in flight per group (U * NV 128-bit loads per
+// lane), MINB resident blocks per SM asked of the compiler (the register budget: 64 for 4, 128 for 2).
+// PF: how many batches ahead the row / column ids are requested.
 // CACHE_DST: edge list is row-sorted, keep the row-side slice in registers.
 // MASKED: the tile is narrower than 4*G*NV floats (ragged last tile).
-template <int G, int NV, int U, bool CACHE_DST, bool MASKED>
-__global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_tile_kernel(const SddmmArgs a) {
+template <int G, int NV, int U, int MINB, int PF, bool CACHE_DST, bool MASKED>
+__global__ void __launch_bounds__(kThreads, MINB) sddmm_tile_kernel(const SddmmArgs a) {
     static_assert(G % U == 0, "U must divide G");
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
@@ -67,43 +73,63 @@ __global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_
     const unsigned gmask = (G == 32) ? 0xffffffffu : (((1u << G) - 1u) << gbase);
     const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
 
-    int colv[NV];
+    // This lane's float4 number i of an edge's slice sits off(i) floats behind the lane's first one:
+    // a compile-time constant (an immediate in the load) unless the tile is ragged, where a float4
+    // beyond the tile's width is read from column 0 instead and zeroed.
+    const int lane_col = (!MASKED || lig * 4 < a.width) ? lig * 4 : 0;
+    int moff[NV];
     bool ok[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        colv[i] = (lig + i * G) * 4;
-        ok[i] = !MASKED || colv[i] < a.width;
-        if (!ok[i]) colv[i] = 0;
+        ok[i] = !MASKED || (lig + i * G) * 4 < a.width;
+        moff[i] = ok[i] ? (lig + i * G) * 4 - lane_col : -lane_col;
     }
+    auto off = [&](int i) { return MASKED ? moff[i] : i * G * 4; };
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    const int ld_src = (int)a.ld_src, ld_dst = (int)a.ld_dst;  // 32 x 32 -> 64 bit multiply per gather
+    const uint64_t keep_policy = fg::l2_keep_policy();
+    const int ld_src = (int)a.ld_src, ld_dst = (int)a.ld_dst;  // 32 x 32 -> 64 bit multiply-add per gather
+    const float* sbase = a.src + lane_col;
+    // the row side is loaded once per row when the list is row-sorted: its base is not worth a register pair
+    const float* dbase_reg = CACHE_DST ? nullptr : a.dst + lane_col;
+#define dbase (CACHE_DST ? a.dst + lane_col : dbase_reg)
     float4 dcache[NV];  // row-side slice of cur_row (meaningful with CACHE_DST only)
 #pragma unroll
     for (int i = 0; i < NV; ++i) dcache[i] = zero4;
     int cur_row = -1;
 
-    // ids of the first batch; each batch then requests the next one's before it starts gathering,
-    // so the id fetch (a DRAM stream) overlaps the previous batch instead of preceding the gathers
+    // Row / column ids are a DRAM stream (one fresh 128-byte line of each per batch), slower to arrive
+    // than a gather from L2: they are requested PF batches before their batch starts, in a small
+    // register ring, so that the wait for them overlaps whole batches of gathers.
     const int64_t first = warp * kBatchesPerWarp * 32;
-    int r_n = 0, c_n = 0;  // padding edges read row 0 / column 0 and are never stored
-    if (first + lane < a.nnz) {
-        r_n = a.row[first + lane];
-        c_n = a.col[first + lane];
+    int r_ring[PF], c_ring[PF];  // padding edges read row 0 / column 0 and are never stored
+#pragma unroll
+    for (int q = 0; q < PF; ++q) {
+        r_ring[q] = 0;
+        c_ring[q] = 0;
+        const int64_t e = first + (int64_t)q * 32 + lane;
+        if (e < a.nnz) {
+            r_ring[q] = fg::ld_stream(a.row + e);
+            c_ring[q] = fg::ld_stream(a.col + e);
+        }
     }
+    static_assert(kBatchesPerWarp % PF == 0 && FG_SDDMM_UNROLL % PF == 0, "PF must divide the unroll factor");
+#pragma unroll kBatchUnroll
     for (int b = 0; b < kBatchesPerWarp; ++b) {
+      {
+        const int q = b % PF;  // a compile-time constant after unrolling
         const int64_t e0 = first + (int64_t)b * 32;
         if (e0 >= a.nnz) break;  // warp-uniform
         const int64_t e = e0 + lane;
         const bool valid = e < a.nnz;
-        const int r_l = r_n, c_l = c_n;
-        r_n = 0;
-        c_n = 0;
-        if (b + 1 < kBatchesPerWarp && e + 32 < a.nnz) {
-            r_n = a.row[e + 32];
-            c_n = a.col[e + 32];
+        const int r_l = r_ring[q], c_l = c_ring[q];
+        r_ring[q] = 0;
+        c_ring[q] = 0;
+        if (b + PF < kBatchesPerWarp && e + 32 * PF < a.nnz) {
+            r_ring[q] = fg::ld_stream(a.row + e + 32 * PF);
+            c_ring[q] = fg::ld_stream(a.col + e + 32 * PF);
         }
         float prev = 0.f;  // earlier tiles' partial dot product
-        if (a.accumulate && valid) prev = a.out[e];
+        if (a.accumulate && valid) prev = fg::ld_stream(a.out + e);
         // Row side.  ONE_ROW: all 32 edges of the batch share a row (the common case in a row-sorted
         // list with long rows): its slice is loaded once, and only if it differs from the previous
         // batch's.  Otherwise a ballot marks where rows change (bit l: edge l starts a new row; always
@@ -129,16 +155,19 @@ __global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_
                 }
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const float* ps = a.src + (int64_t)c[u] * ld_src;
+                    const float* ps = sbase + (int64_t)c[u] * ld_src;
 #pragma unroll
                     for (int i = 0; i < NV; ++i) {
-                        xs[u][i] = fg::ldg4(ps + colv[i]);
+                        xs[u][i] = fg::ldg4_keep(ps + off(i), keep_policy);
                         if (MASKED && !ok[i]) xs[u][i] = zero4;
                     }
                     if (!CACHE_DST) {
-                        const float* pd = a.dst + (int64_t)rr[u] * ld_dst;
+                        const float* pd = dbase + (int64_t)rr[u] * ld_dst;
 #pragma unroll
-                        for (int i = 0; i < NV; ++i) xd[u][i] = fg::ldg4(pd + colv[i]);
+                        for (int i = 0; i < NV; ++i) {
+                            xd[u][i] = fg::ldg4(pd + off(i));
+                            if (MASKED && !ok[i]) xd[u][i] = zero4;
+                        }
                     }
                 }
 #pragma unroll
@@ -147,9 +176,12 @@ __global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_
                     if (CACHE_DST) {
                         if (!ONE_ROW && ((change >> (gbase + s + u)) & 1u)) {  // uniform within the group
                             const int rnew = __shfl_sync(gmask, r_l, gbase + s + u);
-                            const float* pd = a.dst + (int64_t)rnew * ld_dst;
+                            const float* pd = dbase + (int64_t)rnew * ld_dst;
 #pragma unroll
-                            for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
+                            for (int i = 0; i < NV; ++i) {
+                                dcache[i] = fg::ldg4(pd + off(i));
+                                if (MASKED && !ok[i]) dcache[i] = zero4;  // 0 * 0, never 0 * (a stray Inf or NaN)
+                            }
                         }
 #pragma unroll
                         for (int i = 0; i < NV; ++i) acc = dot4(acc, xs[u][i], dcache[i]);
@@ -163,13 +195,13 @@ __global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_
                 // on a lane holds, for the chunk's edge picked by the lane's low bits, the sum over
                 // the 2^k lanes that differ from it in those bits
 #pragma unroll
-                for (int off = 1; off < U; off <<= 1) {
-                    const bool upper = (lig & off) != 0;
+                for (int off2 = 1; off2 < U; off2 <<= 1) {
+                    const bool upper = (lig & off2) != 0;
 #pragma unroll
-                    for (int i = 0; i < U / (2 * off); ++i) {
+                    for (int i = 0; i < U / (2 * off2); ++i) {
                         const float send = upper ? pc[2 * i] : pc[2 * i + 1];
                         const float keep = upper ? pc[2 * i + 1] : pc[2 * i];
-                        pc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                        pc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off2);
                     }
                 }
                 r[s / U] = pc[0];
@@ -179,9 +211,12 @@ __global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_
         if (CACHE_DST && __all_sync(0xffffffffu, r_l == r_first)) {
             if (r_first != cur_row) {
                 cur_row = r_first;
-                const float* pd = a.dst + (int64_t)r_first * ld_dst;
+                const float* pd = dbase + (int64_t)r_first * ld_dst;
 #pragma unroll
-                for (int i = 0; i < NV; ++i) dcache[i] = fg::ldg4(pd + colv[i]);
+                for (int i = 0; i < NV; ++i) {
+                                dcache[i] = fg::ldg4(pd + off(i));
+                                if (MASKED && !ok[i]) dcache[i] = zero4;  // 0 * 0, never 0 * (a stray Inf or NaN)
+                            }
             }
             run_batch(std::true_type{});
         } else {
@@ -191,18 +226,20 @@ __global__ void __launch_bounds__(kThreads, (NV >= 2 && G == 32) ? 2 : 4) sddmm_
 
         // remaining steps across the chunks: afterwards r[0] on lane i of the group is edge i's total
 #pragma unroll
-        for (int off = U; off < G; off <<= 1) {
-            const bool upper = (lig & off) != 0;
-            const int h = off / U;
+        for (int off2 = U; off2 < G; off2 <<= 1) {
+            const bool upper = (lig & off2) != 0;
+            const int h = off2 / U;
 #pragma unroll
             for (int i = 0; i < G / U / (2 * h); ++i) {
                 const float send = upper ? r[2 * i] : r[2 * i + 1];
                 const float keep = upper ? r[2 * i + 1] : r[2 * i];
-                r[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                r[i] = keep + __shfl_xor_sync(0xffffffffu, send, off2);
             }
         }
-        if (valid) a.out[e] = prev + r[0];
+        if (valid) fg::st_stream(a.out + e, prev + r[0]);
+      }
     }
+#undef dbase
 }
 
 // Any d, any alignment: a warp per 32 edges, lanes stride over the feature columns.
@@ -322,40 +359,64 @@ sddmm_exact_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ 
     }
 }
 
-template <int G, int NV, int U>
+#ifndef FG_SDDMM_PF
+#define FG_SDDMM_PF 1
+#endif
+
+template <int G, int NV, int U, int MINB>
 int launch_tile(const SddmmArgs& a, bool cache_dst, bool masked, unsigned blocks, cudaStream_t s) {
     // Variants that hold more live registers (both rows gathered per edge; masked loads) keep
     // half as many edges in flight so that they stay within the register budget.
     constexpr int UH = U > 1 ? U / 2 : 1;
     if (cache_dst) {
         if (masked)
-            sddmm_tile_kernel<G, NV, UH, true, true><<<blocks, kThreads, 0, s>>>(a);
+            sddmm_tile_kernel<G, NV, UH, MINB, FG_SDDMM_PF, true, true><<<blocks, kThreads, 0, s>>>(a);
         else
-            sddmm_tile_kernel<G, NV, U, true, false><<<blocks, kThreads, 0, s>>>(a);
+            sddmm_tile_kernel<G, NV, U, MINB, FG_SDDMM_PF, true, false><<<blocks, kThreads, 0, s>>>(a);
     } else {
         if (masked)
-            sddmm_tile_kernel<G, NV, UH, false, true><<<blocks, kThreads, 0, s>>>(a);
+            sddmm_tile_kernel<G, NV, UH, MINB, FG_SDDMM_PF, false, true><<<blocks, kThreads, 0, s>>>(a);
         else
-            sddmm_tile_kernel<G, NV, UH, false, false><<<blocks, kThreads, 0, s>>>(a);
+            sddmm_tile_kernel<G, NV, UH, MINB, FG_SDDMM_PF, false, false><<<blocks, kThreads, 0, s>>>(a);
     }
     FG_CUDA_TRY(cudaGetLastError());
     fg::count_launches(1);
     return FG_OK;
 }
 
+// Lane layout per tile width: G, NV, U, MINB.  Overridable at build time (kernel sweeps).
+#ifndef FG_Q8_G
+#define FG_Q8_G 8
+#define FG_Q8_NV 1
+#define FG_Q8_U 8
+#define FG_Q8_MINB 4
+#endif
+#ifndef FG_Q16_G  // 64-float tiles: 4 edges per warp step measured fastest
+#define FG_Q16_G 8
+#define FG_Q16_NV 2
+#define FG_Q16_U 4
+#define FG_Q16_MINB 4
+#endif
+#ifndef FG_Q32_G
+#define FG_Q32_G 32
+#define FG_Q32_NV 1
+#define FG_Q32_U 8
+#define FG_Q32_MINB 4
+#endif
+
 // One tile of `width` floats (a multiple of 4, at most 512).
 int launch_width(const SddmmArgs& a, bool cache, unsigned blocks, cudaStream_t s) {
     const int q = (a.width + 3) / 4;  // float4 per edge in this tile
-#define FG_SDDMM(G, NV, U) return launch_tile<G, NV, U>(a, cache, q != (G) * (NV), blocks, s)
-    if (q <= 1) FG_SDDMM(1, 1, 1);
-    if (q <= 2) FG_SDDMM(2, 1, 2);
-    if (q <= 4) FG_SDDMM(4, 1, 4);
-    if (q <= 8) FG_SDDMM(8, 1, 8);
-    if (q <= 16) FG_SDDMM(8, 2, 4);  // 64-float tiles: 4 edges per warp step measured fastest
-    if (q <= 32) FG_SDDMM(32, 1, 8);
-    if (q <= 64) FG_SDDMM(32, 2, 4);
-    if (q <= 96) FG_SDDMM(32, 3, 2);
-    FG_SDDMM(32, 4, 2);
+#define FG_SDDMM(G, NV, U, MINB) return launch_tile<G, NV, U, MINB>(a, cache, q != (G) * (NV), blocks, s)
+    if (q <= 1) FG_SDDMM(1, 1, 1, 4);
+    if (q <= 2) FG_SDDMM(2, 1, 2, 4);
+    if (q <= 4) FG_SDDMM(4, 1, 4, 4);
+    if (q <= 8) FG_SDDMM(FG_Q8_G, FG_Q8_NV, FG_Q8_U, FG_Q8_MINB);
+    if (q <= 16) FG_SDDMM(FG_Q16_G, FG_Q16_NV, FG_Q16_U, FG_Q16_MINB);
+    if (q <= 32) FG_SDDMM(FG_Q32_G, FG_Q32_NV, FG_Q32_U, FG_Q32_MINB);
+    if (q <= 64) FG_SDDMM(32, 2, 4, 2);
+    if (q <= 96) FG_SDDMM(32, 3, 2, 2);
+    FG_SDDMM(32, 4, 2, 2);
 #undef FG_SDDMM
 }
 

@@ -62,7 +62,7 @@ struct Slice;
 template <>
 struct Slice<4> {
     float4 v;
-    __device__ __forceinline__ void load(const float* p) { v = fg::ldg4(p); }
+    __device__ __forceinline__ void load(const float* p, uint64_t policy) { v = fg::ldg4_keep(p, policy); }
     __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
     __device__ __forceinline__ void axpy(float a, const Slice& x) {
         v.x = fg::mul_then_add(v.x, a, x.v.x);
@@ -87,7 +87,7 @@ struct Slice<4> {
 template <>
 struct Slice<1> {
     float v;
-    __device__ __forceinline__ void load(const float* p) { v = __ldg(p); }
+    __device__ __forceinline__ void load(const float* p, uint64_t) { v = __ldg(p); }
     __device__ __forceinline__ void zero() { v = 0.f; }
     __device__ __forceinline__ void axpy(float a, const Slice& x) { v = fg::mul_then_add(v, a, x.v); }
     __device__ __forceinline__ void add(const Slice& x) { v = __fadd_rn(v, x.v); }
@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(kThreads, SHORT ? 6 : 2) spmm_rows_kernel(cons
 
     Slice<VEC> total;
     total.zero();
+    const uint64_t keep_policy = fg::l2_keep_policy();
 
     for (int k = 0; k < (DDS ? a.parts : 1); ++k) {
         int start = extent.x, len = extent.y;
@@ -146,16 +147,16 @@ __global__ void __launch_bounds__(kThreads, SHORT ? 6 : 2) spmm_rows_kernel(cons
         int my_c = -1;
         float my_v = 0.f;
         if (lig < len) {
-            my_c = a.idx[start + lig];
-            if (!UNIT) my_v = a.vals[start + lig];
+            my_c = fg::ld_stream(a.idx + start + lig);
+            if (!UNIT) my_v = fg::ld_stream(a.vals + start + lig);
         }
         for (int base = 0; base < max_len; base += G) {
             // next batch of indices / values, one iteration ahead of its use
             int nx_c = -1;
             float nx_v = 0.f;
             if (base + G + lig < len) {
-                nx_c = a.idx[start + base + G + lig];
-                if (!UNIT) nx_v = a.vals[start + base + G + lig];
+                nx_c = fg::ld_stream(a.idx + start + base + G + lig);
+                if (!UNIT) nx_v = fg::ld_stream(a.vals + start + base + G + lig);
             }
 #pragma unroll
             for (int j0 = 0; j0 < G; j0 += CH) {
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(kThreads, SHORT ? 6 : 2) spmm_rows_kernel(cons
                 // CH gathers are in flight before the first dependent add.
 #pragma unroll
                 for (int j = 0; j < CH; ++j)
-                    xr[j].load(xbase + (int64_t)(c[j] < 0 ? 0 : c[j]) * ldx32);
+                    xr[j].load(xbase + (int64_t)(c[j] < 0 ? 0 : c[j]) * ldx32, keep_policy);
                 // Branch-free commit: a branch here would let the compiler sink each load
                 // next to its use and serialise the gathers.
 #pragma unroll
@@ -218,9 +219,15 @@ constexpr int kLongWarps = 4;                // warps (= units) per block
 constexpr int kLongThreads = kLongWarps * 32;
 constexpr int kSlotFloats = kRingNnz * 32 + kRingNnz;  // 32 slices of 32 floats + 32 values
 constexpr int kLongSmemBytes = kLongWarps * kRingStages * kSlotFloats * 4;
-__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src, uint64_t policy) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+#if FG_HINT_KEEP
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "l"(policy)
+                 : "memory");
+#else
+    (void)policy;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+#endif
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
@@ -290,14 +297,15 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
     const bool piece_ok = col0 + piece * 4 < a.d;  // ragged last tile (d % 4 == 0)
     const float* xpiece = a.x + col0 + piece * 4;
     const int ldx32 = (int)a.ldx;
+    const uint64_t keep_policy = fg::l2_keep_policy();
 
     auto fetch_ids = [&](int stage, int& c, float& v) {  // nonzero `lane` of `stage`
         const int k = stage * kRingNnz + lane;
         c = -1;
         v = 0.f;
         if (k < len) {
-            c = a.idx[start + k];
-            if (!UNIT) v = a.vals[start + k];
+            c = fg::ld_stream(a.idx + start + k);
+            if (!UNIT) v = fg::ld_stream(a.vals + start + k);
         }
     };
     auto fill = [&](int stage, int c_mine, float v_mine) {
@@ -308,7 +316,7 @@ __global__ void __launch_bounds__(kLongThreads) spmm_long_rows_kernel(const Spmm
             for (int i = 0; i < kRingNnz / 4; ++i) {
                 const int nz = i * 4 + sub;
                 const int c = __shfl_sync(0xffffffffu, c_mine, nz);
-                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * ldx32);
+                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * ldx32, keep_policy);
             }
         }
         cp_async_commit();  // one group per stage, empty past the end, so the wait count is fixed
@@ -416,14 +424,15 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
     const bool piece_ok = col0 + piece * 4 < a.d;
     const float* xpiece = a.x + col0 + piece * 4;
     const int ldx32 = (int)a.ldx;
+    const uint64_t keep_policy = fg::l2_keep_policy();
 
     auto fetch_ids = [&](int i, int& c, float& v) {  // nonzero `lane` of local stage i
         const int k = row_stage(i) * kRingNnz + lane;
         c = -1;
         v = 0.f;
         if (k < len) {  // also false for every stage past the row's end
-            c = a.idx[start + k];
-            if (!UNIT) v = a.vals[start + k];
+            c = fg::ld_stream(a.idx + start + k);
+            if (!UNIT) v = fg::ld_stream(a.vals + start + k);
         }
     };
     auto fill = [&](int i, int c_mine, float v_mine) {
@@ -434,7 +443,7 @@ __global__ void __launch_bounds__(W * 32) spmm_heavy_rows_kernel(const SpmmArgs 
             for (int j = 0; j < kRingNnz / 4; ++j) {
                 const int nz = j * 4 + sub;
                 const int c = __shfl_sync(0xffffffffu, c_mine, nz);
-                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * ldx32);
+                if (c >= 0 && piece_ok) cp_async16(slot + nz * 32 + piece * 4, xpiece + (int64_t)c * ldx32, keep_policy);
             }
         }
         cp_async_commit();  // one group per local stage, empty past the end
@@ -846,7 +855,11 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     // other kernel instead of idling the GPU (R-MAT scale 22, d = 128: 7.5 -> 5.7 ms).  When a slice can stay resident
     // the kernels run one after the other: side by side each would evict the slice the other one
     // lives on (measured on the 233K-node graph: up to 25 % slower than in sequence).
+#ifdef FG_PROBE_SIDE_BY_SIDE_ONE_TILE
+    const bool side_by_side = !slice_can_stay_in_l2(n_cols) || d <= tile;
+#else
     const bool side_by_side = !slice_can_stay_in_l2(n_cols);
+#endif
     RowSplit split;
     if (schedule && !dds) split = choose_row_split(*schedule, d, tile, side_by_side);
     // Rows of fewer than 64 nonzeros (the schedule's first threshold) take the SHORT form of the

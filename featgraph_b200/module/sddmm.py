@@ -53,16 +53,45 @@ class SDDMMbase:
                                                 ctypes.byref(sorted_flag),
                                                 dev.stream_ptr(self._device)))
         self._rows_sorted = int(sorted_flag.value)
+        self._plans = {}   # column-block plans by block count (built on first use, freed with the module)
+        self._plan = None  # the plan the current build() uses, or None: plain fg_sddmm_coo_f32
         self._shapes = None
         self._feat_tile = 0
         self._exact = False
         self._staging = None
         self.out = None
 
+    def __del__(self):
+        plans = getattr(self, "_plans", None) or {}
+        for h in plans.values():
+            if h is not None and h.value:
+                try:
+                    dev.lib().fg_sddmm_plan_destroy(h)
+                except Exception:
+                    pass
+        self._plans = {}
+
     def _register(self):
         raise NotImplementedError("Please register target.")
 
-    def _plan(self, input_placeholders, compute_args, schedule_args):
+    def _column_block_plan(self, parts):
+        """The plan for ``parts`` column blocks (built once, kept), or None where the edge list is not in
+        CSR order (rows non-decreasing, column ids ascending within a row) and no plan can be built."""
+        import ctypes
+        if parts not in self._plans:
+            handle = ctypes.c_void_p()
+            with torch.cuda.device(self._device):
+                rc = dev.lib().fg_sddmm_plan_create(dev.ptr(self._adj_row), dev.ptr(self._adj_col), self._num_rows,
+                                                    self._num_cols, self._nnz, int(parts),
+                                                    dev.stream_ptr(self._device), ctypes.byref(handle))
+            if rc == 1 and b"CSR order" in dev.lib().fg_last_error():
+                self._plans[parts] = None  # e.g. unsorted column ids inside rows: the plain call serves
+            else:
+                dev.check(rc)
+                self._plans[parts] = handle
+        return self._plans[parts]
+
+    def _plan_args(self, input_placeholders, compute_args, schedule_args):
         compute_args = dict(compute_args or {})
         schedule_args = dict(schedule_args or {})
         for k in compute_args:
@@ -98,6 +127,10 @@ class SDDMMbase:
                 tile = f
         self._planned_tile = tile
         self._planned_exact = bool(schedule_args.get("exact", self._exact_by_default))
+        # column blocks: 0 = let the library decide, 1 = never, P = that many
+        self._planned_parts = int(schedule_args.get("col_blocks", 0))
+        if self._planned_parts < 0:
+            raise ValueError("col_blocks must be >= 0")
         return src_shape, dst_shape, d, nfp
 
     def _check_schedule(self, schedule_args, nfp):
@@ -106,21 +139,32 @@ class SDDMMbase:
     def build(self, input_placeholders, compute_args, schedule_args):
         """Fix the feature shapes and allocate the (reused) per-edge output (reference :72-92).
         ``schedule_args['exact'] = True`` selects the kernel that sums every dot product in the x86
-        loop's order (bit-identical to it, three to four times slower); ``feat_tile`` sets the L2 tile width."""
-        src_shape, dst_shape, _, _ = self._plan(input_placeholders, compute_args, schedule_args)
+        loop's order (bit-identical to it, three to four times slower); ``feat_tile`` sets the L2 tile width;
+        ``col_blocks`` the number of column blocks of the one-pass traversal (0 = the library decides, 1 = off)."""
+        src_shape, dst_shape, d, _ = self._plan_args(input_placeholders, compute_args, schedule_args)
         self._shapes = (src_shape, dst_shape)
         self._feat_tile = self._planned_tile
         self._exact = self._planned_exact
+        # One pass over column blocks where the column-side matrix is too large for L2 (and no tile width
+        # or exact order was asked for): needs a CSR-ordered edge list, else the tiled call serves.
+        self._plan = None
+        parts = self._planned_parts
+        if parts == 0 and not self._exact and self._feat_tile == 0 and self._rows_sorted:
+            parts = int(dev.lib().fg_sddmm_auto_partitions(self._num_rows, self._num_cols, self._nnz, d))
+        if parts > 1 and not self._exact and self._rows_sorted and d % 4 == 0 and d <= 512:
+            self._plan = self._column_block_plan(parts)
         self.out = torch.zeros((self._nnz,), dtype=torch.float32, device=self._device)
 
     def lower_to_ir(self, input_placeholders, compute_args, schedule_args):
         """Text description of what ``build`` + ``run`` would launch (reference :94-113)."""
-        _, _, d, nfp = self._plan(input_placeholders, compute_args, schedule_args)
+        _, _, d, nfp = self._plan_args(input_placeholders, compute_args, schedule_args)
         return ("featgraph_b200 sddmm: rows=%d cols=%d nnz=%d feat_len=%d num_feat_partitions=%d "
-                "edge_order=%s rows_sorted=%d kernel=fg_sddmm_coo_f32 device=%s"
+                "edge_order=%s rows_sorted=%d kernel=%s device=%s"
                 % (self._num_rows, self._num_cols, self._nnz, d, nfp,
                    "2d(%dx%d)" % (self._num_row_partitions, self._num_col_partitions)
-                   if self._num_row_partitions > 1 else "as_given", self._rows_sorted, self._device))
+                   if self._num_row_partitions > 1 else "as_given", self._rows_sorted,
+                   "fg_sddmm_coo_f32_exact" if self._planned_exact else
+                   "fg_sddmm_coo_f32 (or _planned over column blocks where the matrix exceeds L2)", self._device))
 
     def _launch(self, src, dst, out):
         d = self._shapes[0][1]
@@ -129,6 +173,12 @@ class SDDMMbase:
                                                        dev.ptr(src), 0, dev.ptr(dst), 0, dev.ptr(out),
                                                        self._num_rows, self._num_cols, self._nnz, d, 0,
                                                        dev.stream_ptr(self._device)))
+            return
+        if self._plan is not None:
+            dev.check(dev.lib().fg_sddmm_coo_f32_planned(self._plan, dev.ptr(self._adj_col), dev.ptr(src), 0,
+                                                         dev.ptr(dst), 0, dev.ptr(out), self._num_rows,
+                                                         self._num_cols, self._nnz, d, 0,
+                                                         dev.stream_ptr(self._device)))
             return
         dev.check(dev.lib().fg_sddmm_coo_f32(dev.ptr(self._adj_row), dev.ptr(self._adj_col),
                                              dev.ptr(src), 0, dev.ptr(dst), 0, dev.ptr(out),
@@ -213,7 +263,7 @@ class VanillaSDDMMx86(SDDMMbase):
 
     _compute_keys = ("num_feat_partitions",)
     _exact_by_default = True
-    _schedule_keys = ("num_feat_partitions", "feat_tile", "exact")
+    _schedule_keys = ("num_feat_partitions", "feat_tile", "exact", "col_blocks")
 
     def __init__(self, adj_scipy, num_row_partitions=1, num_col_partitions=1, device=None):
         super().__init__(adj_scipy, num_row_partitions, num_col_partitions, device)
@@ -228,7 +278,7 @@ class VanillaSDDMMcuda(SDDMMbase):
     (python/featgraph/op/vanilla_sddmm.py:79-82) and otherwise has no effect."""
 
     _compute_keys = ()
-    _schedule_keys = ("num_feat_partitions", "num_cuda_blocks", "feat_tile", "exact")
+    _schedule_keys = ("num_feat_partitions", "num_cuda_blocks", "feat_tile", "exact", "col_blocks")
 
     def __init__(self, adj_scipy, device=None):
         super().__init__(adj_scipy, 1, 1, device)

@@ -14,8 +14,8 @@
  *    pointer.  int32 index arrays and fp32 values, as the reference keeps scipy's dtypes
  *    (module/spmm.py:59-64).  Feature matrices are dense row-major; the row stride is d unless a
  *    stride argument says otherwise.
- *  - The caller owns every array.  The library owns only the fg_row_schedule objects it hands
- *    out (freed by fg_row_schedule_destroy), a pair of copy streams and a pool of events per host
+ *  - The caller owns every array.  The library owns only the fg_row_schedule / fg_sddmm_plan objects it
+ *    hands out (freed by their destroy calls), a pair of copy streams and a pool of events per host
  *    thread that uses the host-buffer calls, and one static scratch array (fg_spmm_csr_f32_static).
  *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Device
  *    entry points only enqueue work on it; they do not synchronise.
@@ -179,6 +179,39 @@ int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_
                      const float* d_dst, int64_t ld_dst, float* d_out, int64_t n_rows, int64_t n_cols,
                      int64_t nnz, int32_t d, int32_t rows_sorted, int32_t accumulate, int32_t feat_tile,
                      void* stream);
+
+/* --------------------------------------------------------------------------------------
+ * SDDMM in one pass over column blocks, for feature matrices too large for L2.
+ * fg_sddmm_coo_f32 keeps its gathers in L2 by walking the whole edge list once per feature tile.  This
+ * call cuts the COLUMN range instead - num_col_partitions blocks of ceil(n_cols / P) columns, the column
+ * blocks of the reference's 2-D edge partitioning (python/featgraph/util/adj_partitioning.py:100-101,
+ * the num_col_partitions knob of VanillaSDDMMx86, module/sddmm.py:169) used as a traversal order - and
+ * visits the edges block by block, so that only ceil(n_cols / P) whole rows of src are gathered from at
+ * a time.  Every edge is visited once: ids are read once, out[e] is written once.  Unlike the reference's
+ * partitioning nothing is permuted: out keeps the caller's edge order, no edge_mapping is needed.
+ *   plan   built once per adjacency by fg_sddmm_plan_create from the SAME d_row / d_col the calls use
+ *          (16 bytes of device memory per 32 edges plus 16 per non-empty (block, row) run).  It needs
+ *          a CSR-ordered edge list: rows non-decreasing, column ids ascending within a row; anything
+ *          else is refused with FG_ERR_INVALID_ARGUMENT (use fg_sddmm_coo_f32).  Synchronises `stream`.
+ *   fg_sddmm_auto_partitions   the block count that makes one block of src (ceil(n_cols / P) rows of d
+ *          floats) fit the share of L2 that stays resident, or 1 where fg_sddmm_coo_f32 is the better
+ *          call: the matrix fits L2 anyway, d > 512, d % 4 != 0, or rows so short that a (block, row)
+ *          run would hold only a few edges.
+ * The planned call needs d <= 512, d and the strides multiples of 4, 16-byte aligned matrices.
+ * Values: FMAs within a lane, a fixed tree across the 32 lanes of a warp; within fp32 rounding of d terms
+ * of the sequential sum (and of fg_sddmm_coo_f32, whose tree differs).
+ * -------------------------------------------------------------------------------------- */
+typedef struct fg_sddmm_plan fg_sddmm_plan;
+int32_t fg_sddmm_auto_partitions(int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d);
+int fg_sddmm_plan_create(const int32_t* d_row, const int32_t* d_col, int64_t n_rows, int64_t n_cols,
+                         int64_t nnz, int32_t num_col_partitions, void* stream, fg_sddmm_plan** out_plan);
+int32_t fg_sddmm_plan_partitions(const fg_sddmm_plan* plan);
+/* Number of 32-edge batches the plan holds. */
+int64_t fg_sddmm_plan_batches(const fg_sddmm_plan* plan);
+void fg_sddmm_plan_destroy(fg_sddmm_plan* plan);
+int fg_sddmm_coo_f32_planned(const fg_sddmm_plan* plan, const int32_t* d_col, const float* d_src, int64_t ld_src,
+                             const float* d_dst, int64_t ld_dst, float* d_out, int64_t n_rows, int64_t n_cols,
+                             int64_t nnz, int32_t d, int32_t accumulate, void* stream);
 
 /* SDDMM with the reference's x86 summation order, bit for bit: every product and every sum
  * rounded separately, k strictly ascending (python/featgraph/op/vanilla_sddmm.py:43-62 with the

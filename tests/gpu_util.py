@@ -105,3 +105,39 @@ def sddmm_exact(row, col, src, dst):
     torch.cuda.synchronize()
     assert guards_intact(buf), "kernel wrote outside its output"
     return out.cpu().numpy()
+
+
+class SddmmPlan:
+    """fg_sddmm_plan over device row / col arrays (column blocks of ceil(n_cols / parts))."""
+
+    def __init__(self, row_dev, col_dev, n_rows, n_cols, parts):
+        self.h = ctypes.c_void_p()
+        _native.check(_native.lib().fg_sddmm_plan_create(p(row_dev), p(col_dev), n_rows, n_cols, row_dev.numel(),
+                                                         parts, stream(), ctypes.byref(self.h)))
+
+    def close(self):
+        if self.h.value:
+            _native.lib().fg_sddmm_plan_destroy(self.h)
+            self.h = ctypes.c_void_p()
+
+    def __del__(self):
+        self.close()
+
+
+def sddmm_planned(row, col, src, dst, parts, accumulate_onto=None):
+    """fg_sddmm_coo_f32_planned on numpy inputs (a CSR-ordered edge list); returns the numpy per-edge output."""
+    L = _native.lib()
+    n_cols, d = src.shape
+    n_rows = dst.shape[0]
+    rr, cc, ss, dd = dev(row, np.int32), dev(col, np.int32), dev(src, np.float32), dev(dst, np.float32)
+    buf, out = guarded(len(row))
+    if accumulate_onto is not None:
+        out.copy_(torch.from_numpy(accumulate_onto).cuda())
+    plan = SddmmPlan(rr, cc, n_rows, n_cols, parts)
+    assert L.fg_sddmm_plan_partitions(plan.h) == parts
+    _native.check(L.fg_sddmm_coo_f32_planned(plan.h, p(cc), p(ss), 0, p(dd), 0, p(out), n_rows, n_cols, len(row), d,
+                                             1 if accumulate_onto is not None else 0, stream()))
+    torch.cuda.synchronize()
+    assert guards_intact(buf), "kernel wrote outside its output"
+    plan.close()
+    return out.cpu().numpy()

@@ -23,6 +23,13 @@ def main():
         check_graph(graph, rank, world, device)
     dist.barrier()
     if rank == 0:
+        print("MULTI_GPU_SMALL_OK world=%d" % world, flush=True)
+    if os.environ.get("FG_MULTI_GPU_FULL_SIZE", "1") != "0":
+        check_full_size_shard(rank, world, device)
+        dist.barrier()
+        if rank == 0:
+            print("MULTI_GPU_FULL_SIZE_OK world=%d" % world, flush=True)
+    if rank == 0:
         print("MULTI_GPU_OK world=%d" % world, flush=True)
     dist.destroy_process_group()
 
@@ -68,6 +75,55 @@ def check_graph(graph, rank, world, device):
         want_e = oracle.sddmm(coo.row, coo.col, x, y)[adj.indptr[lo]:adj.indptr[hi]]
         np.testing.assert_allclose(e, want_e, rtol=1e-5, atol=1e-4)
     assert spmm.padded == (graph == "power-law"), (graph, bounds)
+
+
+def check_full_size_shard(rank, world, device):
+    """The benchmarked configuration on this rank's shard: the 232,965-node / 114,615,892-edge power-law
+    graph, features exchanged by GatheredFeatures.gather_async / wait (as the benchmark's step does), at
+    the narrowest and the widest benchmarked feature length.  Sampled rows of this rank's range (its
+    longest included) against the CPU oracle: SpMM bit for bit, SDDMM within rtol 1e-5 / atol 1e-4."""
+    import oracle
+    from featgraph_b200 import graphgen
+    from featgraph_b200.sharded import GatheredFeatures, ShardedSDDMM, ShardedSpMM
+    from featgraph_b200.util import nnz_balanced_row_ranges
+
+    w = graphgen.WORKLOADS["C2"]
+    n, nnz, seed = w["n"], w["nnz"], w["seed"]
+    deg = graphgen.power_law_degrees(n, nnz, seed)
+    indptr_all = np.zeros(n + 1, dtype=np.int64)
+    np.cumsum(deg, out=indptr_all[1:])
+    bounds = nnz_balanced_row_ranges(indptr_all, world)
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    local = graphgen.power_law_graph(n, nnz, seed, rows=(lo, hi))
+    assert local.nnz == int(indptr_all[hi] - indptr_all[lo])
+    spmm = ShardedSpMM(local, bounds, device=device)
+    sddmm = ShardedSDDMM(local, bounds, device=device)
+    ldeg = np.diff(local.indptr)
+    rng = np.random.default_rng(500 + rank)
+    rows = np.unique(np.concatenate([rng.integers(0, hi - lo, 200), np.argsort(-ldeg)[:4], [0, hi - lo - 1]]))
+    sub_ptr = np.zeros(len(rows) + 1, dtype=np.int32)
+    np.cumsum(ldeg[rows], out=sub_ptr[1:])
+    idx = np.concatenate([np.arange(local.indptr[r], local.indptr[r + 1]) for r in rows])
+    sub_cols = local.indices[idx]
+    row_of = np.repeat(rows + lo, ldeg[rows]).astype(np.int32)  # global row ids
+    for d in (32, 512):
+        x = graphgen.workload_features("C2", n, d, 0)
+        y = graphgen.workload_features("C2", n, d, 1)
+        xl = torch.from_numpy(np.ascontiguousarray(x[lo:hi])).to(device)
+        yl = torch.from_numpy(np.ascontiguousarray(y[lo:hi])).to(device)
+        spmm.build(d)
+        sddmm.build(d)
+        g = GatheredFeatures(bounds, d, device=device)
+        for _ in range(2):  # twice: the exchange buffer and the outputs are reused between steps
+            g.gather_async(xl)
+            g.wait()
+            out = spmm.run(g).cpu().numpy()
+            e = sddmm.run(g, yl).cpu().numpy()
+        want = oracle.spmm_csr(sub_ptr, sub_cols, local.data[idx], x)
+        np.testing.assert_array_equal(out[rows], want)
+        want_e = oracle.sddmm(row_of, sub_cols, x, y)  # column side x (gathered), row side y (local rows)
+        np.testing.assert_allclose(e[idx], want_e, rtol=1e-5, atol=1e-4)
+        del g
 
 
 if __name__ == "__main__":

@@ -105,6 +105,36 @@ def test_c2_full_size_sddmm(oracle, c2_graph):
     np.testing.assert_array_equal(out4, 4.0 * tiled)
 
 
+@pytest.mark.parametrize("d", [32, 128, 256, 512])
+def test_c2_full_size_spmm_at_every_benchmarked_feature_length(oracle, c2_graph, d):
+    """The timed configuration itself, at the feature lengths the d = 64 test above does not cover: at
+    d = 32 the launch hands its longest rows to the ring kernels, from d = 128 up it walks several
+    feature tiles.  Sampled rows (the six longest included) against the oracle, bit for bit."""
+    from featgraph_b200 import graphgen
+    adj = c2_graph
+    n = adj.shape[0]
+    x = graphgen.workload_features("C2", n, d, 0)
+    m = VanillaSpMMcuda(adj)
+    m.build([placeholder((n, d))], {}, {})
+    out = m.run([torch.from_numpy(x).to(m.ctx)]).cpu().numpy()
+    _check_spmm_sample(oracle, adj, x, out, np.random.default_rng(100 + d))
+
+
+@pytest.mark.parametrize("d", [32, 128, 256, 512])
+def test_c2_full_size_sddmm_at_every_benchmarked_feature_length(oracle, c2_graph, d):
+    """SDDMM of the timed configuration at the other feature lengths (from d = 128 up one launch per
+    64-float tile, each adding to out[e]): sampled rows' edges within rtol 1e-5 / atol 1e-4."""
+    from featgraph_b200 import graphgen
+    adj = c2_graph
+    n = adj.shape[0]
+    src = graphgen.workload_features("C2", n, d, 0)
+    dst = graphgen.workload_features("C2", n, d, 1)
+    m = VanillaSDDMMcuda(adj.tocoo())
+    m.build([placeholder((n, d)), placeholder((n, d))], {}, {})
+    out_e = m.run([torch.from_numpy(src).to(m.ctx), torch.from_numpy(dst).to(m.ctx)]).cpu().numpy()
+    _check_sddmm_sample(oracle, adj, src, dst, out_e, np.random.default_rng(200 + d))
+
+
 def test_c2_full_size_sddmm_exact_order(oracle, c2_graph):
     """d = 128 on the full graph: the exact-order kernel runs in two 64-float column windows here
     (the second continues the first one's sequential sum) and still equals the oracle bit for bit."""
@@ -155,6 +185,18 @@ def test_c4_rmat_aggregate_then_score(oracle):
     sddmm = VanillaSDDMMcuda(adj.tocoo())
     sddmm.build([placeholder((n, 128)), placeholder((n, 128))], {}, {})
     # column side = Y (indexed by col), row side = H (indexed by row)
-    out_e = sddmm.run([torch.from_numpy(y).to(sddmm.ctx), h_dev]).cpu().numpy()
+    yd = torch.from_numpy(y).to(sddmm.ctx)
+    out_e = sddmm.run([yd, h_dev]).cpu().numpy()
     assert out_e.shape == (adj.nnz,)
+    # H's entries are in the hundreds (sums over up to 162,792 neighbours), so the stated atol of 1e-4
+    # - written for operands in [-1, 1) - is scaled by the size of the products it stands for
     _check_sddmm_sample(oracle, adj, y, h, out_e, rng, n_random=2000, unit_scale=False)
+    # and the check that needs no bound: the exact-order kernel on the same inputs equals the oracle's
+    # sequential sum bit for bit on the sampled rows' edges
+    sddmm.build([placeholder((n, 128)), placeholder((n, 128))], {}, {"exact": True})
+    exact_e = sddmm.run([yd, h_dev]).cpu().numpy()
+    deg = np.diff(adj.indptr)
+    rows = np.unique(np.concatenate([np.random.default_rng(44).integers(0, n, 2000), np.argsort(-deg)[:3]]))
+    _, cols, _, idx = _sub_csr(adj, rows)
+    row_of = np.repeat(rows, deg[rows]).astype(np.int32)
+    np.testing.assert_array_equal(exact_e[idx], oracle.sddmm(row_of, cols, y, h))

@@ -259,3 +259,33 @@ def test_benchmark_scripts_read_npz_datasets(tmp_path):
                            timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
         assert "average time of 5 runs" in r.stdout
+
+
+def test_sddmm_module_column_blocks(oracle):
+    """``col_blocks``: the one-pass traversal over column blocks gives the dot products of the tiled call,
+    in the caller's edge order; an edge list that is not in CSR order quietly takes the tiled call."""
+    from featgraph_b200 import graphgen
+    adj = graphgen.power_law_graph(400, 400 * 30, seed=17, kmax=350)
+    coo = adj.tocoo()
+    n, d = 400, 256
+    src, dst = graphgen.uniform_features((n, d), seed=18), graphgen.uniform_features((n, d), seed=19)
+    want = oracle.sddmm(coo.row, coo.col, src, dst)
+    m = VanillaSDDMMcuda(coo)
+    s, t = torch.from_numpy(src).to(m.ctx), torch.from_numpy(dst).to(m.ctx)
+    m.build([placeholder((n, d)), placeholder((n, d))], {}, {})
+    assert m._plan is None  # small enough for L2: nothing to block
+    plain = m.run([s, t]).cpu().numpy().copy()
+    m.build([placeholder((n, d)), placeholder((n, d))], {}, {"col_blocks": 5})
+    assert m._plan is not None
+    blocked = m.run([s, t]).cpu().numpy()
+    np.testing.assert_allclose(blocked, want, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(blocked, plain, rtol=RTOL, atol=ATOL)
+    assert m.measure_average_time([s, t], 2) > 0
+    # shuffled edge list: no plan can be built, the result is still right and in the caller's order
+    perm = np.random.default_rng(1).permutation(coo.nnz)
+    import scipy.sparse as sp
+    shuffled = sp.coo_matrix((coo.data[perm], (coo.row[perm], coo.col[perm])), shape=coo.shape)
+    m2 = VanillaSDDMMcuda(shuffled)
+    m2.build([placeholder((n, d)), placeholder((n, d))], {}, {"col_blocks": 5})
+    assert m2._plan is None
+    np.testing.assert_allclose(m2.run([s, t]).cpu().numpy(), want[perm], rtol=RTOL, atol=ATOL)

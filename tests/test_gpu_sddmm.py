@@ -161,3 +161,78 @@ def test_coo_validate_reports_order_and_range():
     r2 = G.dev(np.array([0, 2, 1, 2], np.int32))
     assert L.fg_coo_validate(G.p(r2), G.p(c), 3, 4, 4, ctypes.byref(flag), G.stream()) == 0 and flag.value == 0
     assert L.fg_coo_validate(G.p(r2), G.p(c), 2, 4, 4, ctypes.byref(flag), G.stream()) == 4
+
+
+# ---- one pass over column blocks (fg_sddmm_coo_f32_planned) ------------------------------------
+
+@pytest.mark.parametrize("d", [4, 36, 64, 128, 132, 200, 256, 384, 500, 512])
+@pytest.mark.parametrize("parts", [1, 2, 3, 7])
+def test_column_block_plan_gives_the_same_dot_products(oracle, d, parts):
+    """Every edge is visited once, in block-major order, and lands at its own place in the caller's edge
+    order: rows of very different lengths (empty ones, single edges, runs longer than one 32-edge batch),
+    a column count that the block count does not divide."""
+    import gpu_util as G
+    from featgraph_b200 import graphgen
+    adj = graphgen.power_law_graph(301, 301 * 40, seed=300 + parts, kmax=290).tolil()
+    adj[7, :] = 0
+    adj[300, :] = 0
+    adj = adj.tocsr()
+    adj.eliminate_zeros()
+    adj.sort_indices()
+    coo = adj.tocoo()
+    row, col = coo.row.astype(np.int32), coo.col.astype(np.int32)
+    src, dst = _feat(301, d, 11), _feat(301, d, 12)
+    want = oracle.sddmm(row, col, src, dst)
+    np.testing.assert_allclose(G.sddmm_planned(row, col, src, dst, parts), want, rtol=RTOL, atol=ATOL)
+
+
+def test_column_block_plan_is_exact_on_integer_valued_features():
+    """With small integer features every product and partial sum is exact, so any summation tree must give
+    the same bits as numpy: a test of WHICH edges and columns are combined, free of rounding."""
+    import gpu_util as G
+    rng = np.random.default_rng(5)
+    coo = sp.random(180, 1000, density=0.08, format="csr", random_state=9).tocoo()  # wide: many column blocks
+    row, col = coo.row.astype(np.int32), coo.col.astype(np.int32)
+    for d in (128, 200, 512):
+        src = rng.integers(-4, 5, (1000, d)).astype(np.float32)
+        dst = rng.integers(-4, 5, (180, d)).astype(np.float32)
+        want = (src[col] * dst[row]).sum(-1)
+        for parts in (2, 5, 16):
+            np.testing.assert_array_equal(G.sddmm_planned(row, col, src, dst, parts), want)
+        # accumulate adds to what out holds
+        base = rng.integers(-100, 100, len(row)).astype(np.float32)
+        np.testing.assert_array_equal(G.sddmm_planned(row, col, src, dst, 3, accumulate_onto=base), base + want)
+
+
+def test_column_block_plan_refuses_what_it_cannot_serve():
+    import ctypes
+    import gpu_util as G
+    from featgraph_b200 import _native
+    L = _native.lib()
+    coo = sp.random(50, 60, density=0.3, format="csr", random_state=3).tocoo()
+    row, col = coo.row.astype(np.int32), coo.col.astype(np.int32)
+    h = ctypes.c_void_p()
+    # columns descending inside rows
+    rc = L.fg_sddmm_plan_create(G.p(G.dev(row)), G.p(G.dev(col[::-1].copy())), 50, 60, len(row), 2, G.stream(),
+                                ctypes.byref(h))
+    assert rc == 1 and b"CSR order" in L.fg_last_error() and not h.value
+    # rows not sorted
+    perm = np.random.default_rng(0).permutation(len(row))
+    rc = L.fg_sddmm_plan_create(G.p(G.dev(row[perm])), G.p(G.dev(col[perm])), 50, 60, len(row), 2, G.stream(),
+                                ctypes.byref(h))
+    assert rc == 1 and b"CSR order" in L.fg_last_error()
+    # a plan of another adjacency, an unsupported feature length
+    rr, cc = G.dev(row), G.dev(col)
+    plan = G.SddmmPlan(rr, cc, 50, 60, 2)
+    src, dst, out = G.dev(_feat(60, 8, 1)), G.dev(_feat(50, 8, 2)), G.dev(np.zeros(len(row), np.float32))
+    rc = L.fg_sddmm_coo_f32_planned(plan.h, G.p(cc), G.p(src), 0, G.p(dst), 0, G.p(out), 50, 60, len(row) - 1, 8, 0,
+                                    G.stream())
+    assert rc == 1 and b"rebuild the plan" in L.fg_last_error()
+    rc = L.fg_sddmm_coo_f32_planned(plan.h, G.p(cc), G.p(src), 0, G.p(dst), 0, G.p(out), 50, 60, len(row), 6, 0,
+                                    G.stream())
+    assert rc == 1 and b"multiples of 4" in L.fg_last_error()
+    plan.close()
+    # where the plain call is the better one, the library says so
+    assert L.fg_sddmm_auto_partitions(1000, 1000, 50_000, 64) == 1          # fits L2
+    assert L.fg_sddmm_auto_partitions(1 << 22, 1 << 22, 1 << 27, 128) == 1  # rows far too short per block
+    assert L.fg_sddmm_auto_partitions(232_965, 232_965, 114_615_892, 512) >= 4
