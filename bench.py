@@ -152,44 +152,90 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # CPU leg: the oracle (a restatement of the reference's x86 loop nests) timed on host cores.
 # ----------------------------------------------------------------------------------------------
-def cpu_reference_rates(adj, d, sddmm_edges, runs):
-    """GFLOP/s of the restated x86 path on a bounded sample: SpMM on the whole graph at feature
-    length d with every host thread (row-parallel, with the layout copies the reference's timed
-    function contains); SDDMM single-threaded, as the reference's x86 schedule is, on the first
-    ``sddmm_edges`` edges.  One warm-up run each, then the mean of ``runs``."""
-    import oracle
-    from featgraph_b200 import graphgen
-    n = adj.shape[0]
-    x = graphgen.workload_features(WORKLOAD, n, d, 0)
-    y = graphgen.workload_features(WORKLOAD, n, d, 1)
-    out = np.empty((n, d), dtype=np.float32)
+SDDMM_SAMPLE_DIV = 64  # the single-threaded SDDMM is timed on the first nnz / 64 edges
 
-    def timed(fn):
-        fn()
-        t0 = time.perf_counter()
-        for _ in range(runs):
+
+class CpuStep:
+    """One bounded sample of the step on the host cores, as the reference's x86 path would run it: at
+    EVERY feature length of the step, SpMM on the whole graph with every host thread (row-parallel, with
+    the layout copies the reference's timed function contains, python/featgraph/op/vanilla_spmm.py:41-62)
+    and SDDMM on ONE thread (the reference's x86 SDDMM schedule has no parallel loop,
+    python/featgraph/op/vanilla_sddmm.py:66-74) on the first nnz / 64 edges.  The step rate is formed
+    from all feature lengths: FLOPs of a full step / (sum of SpMM times + sum of SDDMM sample times scaled
+    to all edges)."""
+
+    def __init__(self, adj, dims):
+        import oracle
+        from featgraph_b200 import graphgen
+        self.oracle, self.adj, self.dims = oracle, adj, dims
+        n = adj.shape[0]
+        self.ne = max(1, adj.nnz // SDDMM_SAMPLE_DIV)
+        self.row = np.repeat(np.arange(n, dtype=np.int32), np.diff(adj.indptr))[:self.ne]
+        self.col = adj.indices[:self.ne]
+        self.x = {d: graphgen.workload_features(WORKLOAD, n, d, 0) for d in dims}
+        self.y = {d: graphgen.workload_features(WORKLOAD, n, d, 1) for d in dims}
+        self.out = {d: np.empty((n, d), dtype=np.float32) for d in dims}
+        self.oe = np.empty(self.ne, dtype=np.float32)
+        self.threads = oracle.num_threads()
+
+    def run(self):
+        """One pass over every feature length; returns {d: (spmm seconds, sddmm sample seconds)}."""
+        o, adj, t = self.oracle, self.adj, {}
+        for d in self.dims:
+            t0 = time.perf_counter()
+            o.spmm_csr(adj.indptr, adj.indices, adj.data, self.x[d], with_copies=True, out=self.out[d])
+            t1 = time.perf_counter()
+            o.sddmm(self.row, self.col, self.x[d], self.y[d], threads=1, out=self.oe)
+            t[d] = (t1 - t0, time.perf_counter() - t1)
+        return t
+
+    def summarise(self, runs):
+        """Mean times over ``runs`` (a list of run() results) -> rates."""
+        nnz, scale = self.adj.nnz, self.adj.nnz / float(self.ne)
+        per_d, est_step, sample = {}, 0.0, 0.0
+        for d in self.dims:
+            ts = float(np.mean([r[d][0] for r in runs]))
+            te = float(np.mean([r[d][1] for r in runs]))
+            per_d[d] = {"spmm_s": ts, "spmm_gflops": 2.0 * nnz * d / ts / 1e9,
+                        "sddmm_sample_s": te, "sddmm_gflops": 2.0 * self.ne * d / te / 1e9}
+            est_step += ts + te * scale
+            sample += ts + te
+        flops = sum(2 * 2.0 * nnz * d for d in self.dims)
+        return {"step_gflops": flops / est_step / 1e9, "estimated_full_step_s": est_step, "sample_s": sample,
+                "per_d": per_d, "threads": self.threads, "sddmm_edges": self.ne}
+
+    def extras(self, d=64):
+        """Variants that are not the reference's schedule, once each at one feature length: SpMM with
+        dynamic row scheduling and no layout copies, SDDMM with OpenMP over edges, and scipy's csr.dot on one
+        thread (the ground truth of the reference's own tests, tests/test_module_spmm.py:29)."""
+        o, adj = self.oracle, self.adj
+        d = d if d in self.dims else self.dims[0]
+
+        def timed(fn):
+            t0 = time.perf_counter()
             fn()
-        return (time.perf_counter() - t0) / runs
+            return time.perf_counter() - t0
 
-    t_spmm = timed(lambda: oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x, with_copies=True, out=out))
-    t_spmm_dyn = timed(lambda: oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x, dynamic=True, out=out))
-    ne = min(int(sddmm_edges), adj.nnz)
-    row = np.repeat(np.arange(n, dtype=np.int32), np.diff(adj.indptr))[:ne]
-    col = adj.indices[:ne]
-    oe = np.empty(ne, dtype=np.float32)
-    t_sddmm = timed(lambda: oracle.sddmm(row, col, x, y, threads=1, out=oe))
-    t_sddmm_mt = timed(lambda: oracle.sddmm(row, col, x, y, threads=oracle.num_threads(), out=oe))
-    r_spmm = 2.0 * adj.nnz * d / t_spmm / 1e9
-    r_sddmm = 2.0 * ne * d / t_sddmm / 1e9
-    return {
-        "spmm_gflops": r_spmm, "sddmm_gflops": r_sddmm,
-        "spmm_dynamic_nocopy_gflops": 2.0 * adj.nnz * d / t_spmm_dyn / 1e9,
-        "sddmm_openmp_gflops": 2.0 * ne * d / t_sddmm_mt / 1e9,
-        # a step does the same FLOPs in each op, so the step rate is the harmonic mean
-        "step_gflops": 2.0 / (1.0 / r_spmm + 1.0 / r_sddmm),
-        "seconds": {"spmm": t_spmm, "sddmm_sample": t_sddmm},
-        "threads": oracle.num_threads(), "sddmm_edges": ne, "d": d,
-    }
+        t_dyn = timed(lambda: o.spmm_csr(adj.indptr, adj.indices, adj.data, self.x[d], dynamic=True, out=self.out[d]))
+        t_mt = timed(lambda: o.sddmm(self.row, self.col, self.x[d], self.y[d], threads=self.threads, out=self.oe))
+        rows = max(1, adj.shape[0] // 8)  # scipy is single-threaded: an eighth of the rows bounds its time
+        sub = adj[:rows]
+        t_sp = timed(lambda: sub.dot(self.x[d]))
+        return {"d": d, "spmm_dynamic_nocopy_gflops": 2.0 * adj.nnz * d / t_dyn / 1e9,
+                "sddmm_openmp_gflops": 2.0 * self.ne * d / t_mt / 1e9,
+                "scipy_csr_dot_1thread_gflops": 2.0 * sub.nnz * d / t_sp / 1e9, "scipy_rows": rows}
+
+    def sample_text(self):
+        return ("at each d in %s: SpMM on the whole graph (all %d threads, with the reference's layout copies); "
+                "SDDMM on one thread (the reference's x86 SDDMM has no parallel loop) on the first %d edges, scaled "
+                "to all edges; rate = FLOPs of a full step / estimated full-step time"
+                % (self.dims, self.threads, self.ne))
+
+
+def workload_text(n, nnz):
+    return ("C4 R-MAT graph %d nodes / %d edges: H = A.X then out[e] = dot(H[row e], Y[col e])"
+            if WORKLOAD == "C4" else
+            "C2/C3 power-law graph %d nodes / %d edges: SpMM + SDDMM at each d") % (n, nnz)
 
 
 def run_reference_arm(args):
@@ -209,28 +255,28 @@ def run_reference_arm(args):
     else:
         adj = graphgen.power_law_graph(n, nnz, graphgen.WORKLOADS[WORKLOAD]["seed"], kmax=kmax)
     log("graph built in %.1fs" % (time.time() - t0))
-    d = 64
-    sample_edges = nnz // 16
-    # warm-up steps and timed steps: each "step" is one bounded sample run
-    for _ in range(max(args.warmup - 1, 0)):
-        cpu_reference_rates(adj, d, sample_edges, 1)
+    dims = [int(x) for x in args.dims.split(",")]
+    step = CpuStep(adj, dims)
+    # each "step" is one bounded sample of the whole step (every feature length)
+    for _ in range(max(args.warmup, 0)):
+        step.run()
     t0 = time.perf_counter()
-    r = cpu_reference_rates(adj, d, sample_edges, max(args.steps, 1))
+    runs = [step.run() for _ in range(max(args.steps, 1))]
     wall = time.perf_counter() - t0
+    r = step.summarise(runs)
+    r["extras"] = step.extras()
     line = {
         "impl": "reference", "metric": "spmm_sddmm_gflops", "value": r["step_gflops"], "unit": "GFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * (r["seconds"]["spmm"] + r["seconds"]["sddmm_sample"]),
+        "ms_per_step": 1e3 * wall / max(args.steps, 1),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "C2/C3 power-law graph %d nodes / %d edges: SpMM + SDDMM at each d" % (n, nnz),
-                   "dims": [int(x) for x in args.dims.split(",")], "sample_dims": [d],
+        "config": {"workload": workload_text(n, nnz), "dims": dims,
                    "note": "host cores only (no GPU is used, whatever --gpus says): the CPU restatement of the "
                            "reference's x86 path (the reference itself needs a code generator that is not "
-                           "installed); each step is a bounded sample, SpMM at d=%d on all host threads and "
-                           "SDDMM at d=%d on one thread as in the reference's schedule" % (d, d)},
+                           "installed). ms_per_step is the wall time of one bounded sample; value is the rate of "
+                           "the full step formed from it: " + step.sample_text()},
         "cpu_baseline": {"value": r["step_gflops"], "unit": "GFLOP/s", "cores": r["threads"], "kind": "port",
-                         "sample": "SpMM d=%d whole graph; SDDMM d=%d first %d edges" % (d, d, r["sddmm_edges"]),
-                         "detail": r},
+                         "sample": step.sample_text(), "detail": r},
         "e2e": {"value": r["step_gflops"], "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": wall,
     }
@@ -410,59 +456,61 @@ def run_ours(args):
     # --- end to end: host buffers in, host result out, every step -------------------------------
     e2e = None
     if not args.no_e2e:
+        from featgraph_b200 import sharded
         outs_host = {d: (torch.empty((hi - lo, d), dtype=torch.float32).pin_memory(),
                          torch.empty((local_nnz,), dtype=torch.float32).pin_memory()) for d in dims}
-        h2d = sum(3 * (hi - lo) * d * 4 for d in dims)
+        # bytes copied per step, counted from the tensors the step copies
+        if WORKLOAD == "C4":
+            h2d = sum(2 * (hi - lo) * d * 4 for d in dims) + (sum((hi - lo) * d * 4 for d in dims) if world == 1 else 0)
+        else:
+            h2d = sum((3 if world == 1 else 2) * (hi - lo) * d * 4 for d in dims)
         d2h = sum((hi - lo) * d * 4 + local_nnz * 4 for d in dims)
 
         def e2e_step():
-            for d in dims:
-                xh, yh = feats[d]
-                spmm.build_cached(d, args.feat_tile)
-                sddmm.build_cached(d)
-                if world == 1:
+            if world == 1:
+                for d in dims:
+                    xh, yh = feats[d]
                     # the library's host-buffer calls: copies pipelined against the kernels
                     if WORKLOAD == "C4":  # the second op consumes the first one's host result
+                        spmm.build_cached(d, args.feat_tile)
+                        sddmm.build_cached(d)
                         hh = spmm.module.run_host([xh], out=outs_host[d][0])
                         sddmm.module.run_host([yh, hh], out=outs_host[d][1])
                     else:  # deferred completion: one call's copy-out overlaps the next call
                         e2e_mod[("spmm", d)].run_host([xh], out=outs_host[d][0], wait=False)
                         e2e_mod[("sddmm", d)].run_host([xh, yh], out=outs_host[d][1], wait=False)
-                    continue
-                # N > 1: the same three stages with torch streams around the sharded calls (the
-                # exchange sits between copy-in and kernel): copies in on s_in, results out on s_out
-                xe, se, ye = stage_in[d]
-                with torch.cuda.stream(s_in):
-                    xe.copy_(xh, non_blocking=True)
-                    ev_x = s_in.record_event()
-                    se.copy_(xh, non_blocking=True)
-                    ye.copy_(yh, non_blocking=True)
-                    ev_sy = s_in.record_event()
-                stream.wait_event(ev_x)
-                o1 = spmm.run(xe)
-                ev_k1 = stream.record_event()
-                stream.wait_event(ev_sy)
-                o2 = sddmm.run(ye, o1) if WORKLOAD == "C4" else sddmm.run(se, ye)
-                ev_k2 = stream.record_event()
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_k1)
-                    outs_host[d][0].copy_(o1, non_blocking=True)
-                    s_out.wait_event(ev_k2)
-                    outs_host[d][1].copy_(o2, non_blocking=True)
-            if world == 1:
                 featgraph_b200.host_sync(device)
-            else:
-                s_out.synchronize()
-            stream.synchronize()
+                stream.synchronize()
+                return
+            # N > 1: the sharded layer's host-buffer calls.  Every copy-in and the exchange behind it are
+            # issued first (they need only the copy-in stream), then the kernels, each followed by its
+            # copy-out on the copy-out stream: a step costs about max(copies in, kernels, copies out).
+            for d in dims:
+                e2e_x[d].gather_from_host_async(feats[d][0])
+                if WORKLOAD == "C4":
+                    e2e_y[d].gather_from_host_async(feats[d][1])
+            for d in dims:
+                spmm.build_cached(d, args.feat_tile)
+                sddmm.build_cached(d)
+                if WORKLOAD == "C4":
+                    sharded.wait_for_copy_out(spmm.module.out, device, spmm)
+                    h = spmm.run(e2e_x[d].wait())
+                    sharded.copy_out_async(h, outs_host[d][0], device, spmm)
+                    sharded.wait_for_copy_out(sddmm.module.out, device, sddmm)
+                    o2 = sddmm.run(e2e_y[d].wait(), h)
+                    sharded.copy_out_async(o2, outs_host[d][1], device, sddmm)
+                else:
+                    spmm.run_host(e2e_x[d], outs_host[d][0])
+                    sddmm.run_host(e2e_x[d], feats[d][1], outs_host[d][1])
+            sharded.host_sync(device)
 
+        e2e_mod, e2e_x, e2e_y = {}, {}, {}
         if world > 1:
-            s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
-            stage_in = {d: tuple(torch.empty((hi - lo, d), dtype=torch.float32, device=device) for _ in range(3))
-                        for d in dims}
-
-        # deferred calls must not share staging buffers: one module per (op, d) for the e2e leg
-        e2e_mod = {}
-        if world == 1 and WORKLOAD != "C4":
+            e2e_x = {d: GatheredFeatures(bounds, d, device=device) for d in dims}
+            if WORKLOAD == "C4":
+                e2e_y = {d: GatheredFeatures(bounds, d, device=device) for d in dims}
+        elif WORKLOAD != "C4":
+            # deferred calls must not share staging buffers: one module per (op, d) for the e2e leg
             from featgraph import placeholder as _ph
             from featgraph.module import VanillaSDDMMcuda as _SD, VanillaSpMMcuda as _SP
             coo_local = local_adj.tocoo()
@@ -489,29 +537,46 @@ def run_ours(args):
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": 1e3 * float(dt.item()), "steps": args.e2e_steps,
                "note": "adjacency resident (uploaded at construction, as in the reference); features "
-                       "copied from pinned host memory and results read back every step"
-                       + ("; through run_host (fg_*_host: column windows pipelined, completion deferred to the end of the step)" if world == 1 else "")}
+                       "copied from pinned host memory and results read back every step; "
+                       + ("through run_host (fg_*_host: column windows pipelined, completion deferred to the end of the step)"
+                          if world == 1 else
+                          "through the sharded layer's host-buffer calls (gather_from_host_async / run_host: "
+                          "copy-in and exchange of every feature matrix issued ahead of the kernels, results "
+                          "leaving on a copy-out stream)")}
 
-    # --- per-kernel table and roofline (rank-local time, own rows; max over ranks) --------------
+    # --- order-independent checksum of every output's bits, summed over ranks ---------------------
+    # SpMM sums every element in storage order and SDDMM's tree is fixed per edge, so these values must
+    # be the same at every GPU count (the sharded outputs concatenate to the single-GPU output).
+    checksums = {}
+    for d in dims:
+        for op, t in (("spmm", spmm.out_cache[d][0]), ("sddmm", sddmm.out_cache[d][0])):
+            c = t.contiguous().view(torch.int32).to(torch.int64).sum().reshape(1)
+            if world > 1:
+                dist.all_reduce(c, op=dist.ReduceOp.SUM)
+            checksums["%s_d%d" % (op, d)] = int(c.item())
+
+    # --- per-kernel table and roofline (per GPU: whole-graph bytes / N over the slowest rank's time) --
     peak, peak_kind = measured_peak_gbs()
+    traffic_table, traffic_note = load_ncu_traffic(_native.lib().fg_kernel_signature().decode())
     kernels = []
     for (op, d), ts in sorted(per_kernel.items()):
         ms = float(np.mean(ts))
-        if world > 1:
-            t = torch.tensor([ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        bt = bytes_touched(n, nnz, d)
         g_ms = float(np.mean(gather_ms[(op, d)]))
         if world > 1:
-            t = torch.tensor([g_ms], device=device, dtype=torch.float64)
+            t = torch.tensor([ms, g_ms], device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            g_ms = float(t.item())
+            ms, g_ms = float(t[0].item()), float(t[1].item())
+        bt = bytes_touched(n, nnz, d) / world  # this GPU's share (rows and nonzeros are split evenly)
+        touched = bt / (ms * 1e-3) / 1e9
+        dram = traffic_table.get((op, d))
         kernels.append({
             "op": op, "d": d, "ms": ms, "all_gather_ms": g_ms if world > 1 else 0.0,
             "gflops": 2.0 * nnz * d / (ms * 1e-3) / 1e9,
-            "touched_gbs": bt / (ms * 1e-3) / 1e9, "frac_touched": bt / (ms * 1e-3) / 1e9 / peak,
-            "frac_compulsory": bytes_unique(n, n, nnz, d) / (ms * 1e-3) / 1e9 / peak,
+            "touched_gbs_per_gpu": touched, "frac_touched": touched / peak,
+            "l2_frac": touched / L2_TO_SM_PEAK_GBS,
+            "dram_bytes": dram, "dram_frac": (dram / (ms * 1e-3) / 1e9 / peak) if (dram and world == 1) else None,
+            "frac_compulsory": bytes_unique(n, n, nnz, d) / world / (ms * 1e-3) / 1e9 / peak,
+            "checksum": checksums["%s_d%d" % (op, d)],
         })
     if rank != 0:
         if world > 1:
@@ -519,24 +584,27 @@ def run_ours(args):
         return
     dom = max(kernels, key=lambda k: k["ms"])
     roofline = {
-        "bound": "hbm", "kernel": "%s d=%d (one library call; SDDMM at d>=256 is one launch per 64-float tile)"
-        % (dom["op"], dom["d"]),
-        "achieved": dom["touched_gbs"], "peak": peak, "unit": "GB/s", "frac": dom["frac_touched"],
-        "peak_kind": "of " + peak_kind, "traffic": NCU_TRAFFIC_BYTES.get((dom["op"], dom["d"])),
+        "bound": "hbm", "kernel": "%s d=%d (one library call)" % (dom["op"], dom["d"]),
+        "achieved": dom["touched_gbs_per_gpu"], "peak": peak, "unit": "GB/s", "frac": dom["frac_touched"],
+        "peak_kind": "of " + peak_kind,
+        "traffic": dom["dram_bytes"] if world == 1 else None,
+        "dram_frac": dom["dram_frac"], "l2_frac": dom["l2_frac"], "l2_peak_gbs": L2_TO_SM_PEAK_GBS,
         "compulsory_frac": dom["frac_compulsory"],
-        "algorithmic_bytes": bytes_touched(n, nnz, dom["d"]),
-        "note": "achieved = touched bytes (every nonzero fetches index, value and its feature-row slice) / "
-                "kernel time; gathers served from L2 make it exceed DRAM traffic, see traffic",
+        "algorithmic_bytes": bytes_touched(n, nnz, dom["d"]) / world,
+        "traffic_source": traffic_note,
+        "note": "per GPU. achieved = touched bytes (every nonzero fetches index, value and its feature-row slice) "
+                "/ kernel time: the gathered part of the feature matrix is sized to stay in L2, so this exceeds "
+                "the HBM peak by design; dram_frac = DRAM bytes per call seen by ncu / time / HBM peak is what "
+                "HBM delivers, l2_frac = touched bytes / time / the L2-to-SM rate the ncu captures imply "
+                "(20.6 TB/s at lts__throughput 88 %) is how close the kernel is to the path that bounds it",
     }
     if world > 1:
-        roofline["note"] += "; per-kernel times are the slowest rank's kernel on its shard, with whole-graph bytes"
+        roofline["note"] += "; N > 1: whole-graph bytes / N over the slowest rank's kernel time"
     line = {
         "metric": "spmm_sddmm_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": ("C4 R-MAT graph %d nodes / %d edges: H = A.X then out[e] = dot(H[row e], Y[col e])"
-                                if WORKLOAD == "C4" else
-                                "C2/C3 power-law graph %d nodes / %d edges: SpMM + SDDMM at each d") % (n, nnz),
+        "config": {"workload": workload_text(n, nnz),
                    "dims": dims, "parallelism": "row-sharded x%d (nnz-balanced); each feature matrix all-gathered "
                    "once per step and d, inside the timed region%s" % (world, ", the exchange for the next d running beside "
                    "the current d's kernels" if prefetch else
@@ -544,53 +612,71 @@ def run_ours(args):
                    if world > 1 else "single GPU",
                    "l2_policy": "inputs larger than L2 (CSR arrays %.0f MB per pass; 10 different kernels "
                                 "and feature matrices between repeats of any one)" % (8.0 * nnz / 1e6),
-                   "feat_tile": args.feat_tile or "auto"},
-        "roofline": roofline, "kernels": kernels, "e2e": e2e,
+                   "feat_tile": args.feat_tile or "auto",
+                   "kernel_signature": _native.lib().fg_kernel_signature().decode()},
+        "roofline": roofline, "kernels": kernels, "checksums": checksums, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,
     }
     if not args.no_cpu_baseline and world == 1:
         t0 = time.time()
-        r = cpu_reference_rates(local_adj, 64, nnz // 16, 1)
+        cpu = CpuStep(local_adj, dims)
+        cpu.run()  # warm-up
+        r = cpu.summarise([cpu.run()])
+        r["extras"] = cpu.extras()
         line["cpu_baseline"] = {
             "value": r["step_gflops"], "unit": "GFLOP/s", "cores": r["threads"], "kind": "port",
-            "sample": "SpMM d=64 whole graph (all threads, with the reference's layout copies); SDDMM d=64 "
-                      "first %d edges on one thread (the reference's x86 SDDMM has no parallel loop); "
-                      "1 warm-up + 1 timed run each" % r["sddmm_edges"],
-            "detail": r, "wall_s": time.time() - t0}
+            "sample": cpu.sample_text() + "; 1 warm-up + 1 timed pass", "detail": r, "wall_s": time.time() - t0}
     emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; keyed by (op, feature length).  Absent = not captured.
-NCU_TRAFFIC_BYTES = {
-    ("spmm", 512): 10.6e9,    # spmm_rows_kernel<16,4,0,1,0>, one launch (8 tiles inside)
-    ("spmm", 128): 3.22e9,
-    ("sddmm", 512): 25.7e9,   # sddmm_tile_kernel<8,2,4,1,0>: 8 tile launches of 3.21 GB each
-    ("sddmm", 128): 7.58e9,   # two tile launches
-}
+# The L2 -> SM delivery rate the ncu captures of the SpMM rows kernel imply: 20.6 TB/s delivered at
+# lts__throughput 88 % of peak (profiles/spmm_rows_kernel_c2.md).
+L2_TO_SM_PEAK_GBS = 20600.0 / 0.88
+
+
+def load_ncu_traffic(signature):
+    """DRAM bytes per library call (dram__bytes_read.sum + dram__bytes_write.sum summed over the call's
+    launches) from profiles/ncu_traffic.json, keyed by (op, d) - but only if that file was captured from
+    kernels of the same compile-time shapes as the ones loaded now (fg_kernel_signature)."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        rec = json.load(open(path))
+    except Exception:
+        return {}, "profiles/ncu_traffic.json absent"
+    if rec.get("kernel_signature") != signature:
+        return {}, "profiles/ncu_traffic.json is stale: captured from kernels %r, loaded %r" % (
+            rec.get("kernel_signature"), signature)
+    table = {(e["op"], int(e["d"])): float(e["dram_bytes_per_call"]) for e in rec.get("calls", [])}
+    return table, "profiles/ncu_traffic.json (%s)" % rec.get("captured_by", "ncu")
 
 
 def _install_build_cache(spmm, sddmm):
-    """Keep one output / gather buffer per feature length so that switching d inside a step does
-    not allocate."""
+    """Keep one built state (output, gather buffer, plan) per feature length so that switching d inside
+    a step neither allocates nor re-plans."""
     cache_a, cache_b = {}, {}
+    spmm_keys = ("out", "_feat_shape", "_feat_tile")
+    sddmm_keys = ("out", "_shapes", "_feat_tile", "_exact", "_plan")
 
     def build_spmm(d, tile=0):
         if d not in cache_a:
             spmm.build(d, tile)
-            cache_a[d] = (spmm.module.out, spmm.x_full, spmm.module._feat_shape, spmm.module._feat_tile)
-        spmm.module.out, spmm.x_full, spmm.module._feat_shape, spmm.module._feat_tile = cache_a[d]
+            cache_a[d] = tuple(getattr(spmm.module, k) for k in spmm_keys) + (spmm.x_full,)
+        for k, v in zip(spmm_keys, cache_a[d]):
+            setattr(spmm.module, k, v)
+        spmm.x_full = cache_a[d][-1]
 
     def build_sddmm(d):
         if d not in cache_b:
             sddmm.build(d)
-            cache_b[d] = (sddmm.module.out, sddmm.src_full, sddmm.module._shapes)
-        sddmm.module.out, sddmm.src_full, sddmm.module._shapes = cache_b[d]
+            cache_b[d] = tuple(getattr(sddmm.module, k) for k in sddmm_keys) + (sddmm.src_full,)
+        for k, v in zip(sddmm_keys, cache_b[d]):
+            setattr(sddmm.module, k, v)
+        sddmm.src_full = cache_b[d][-1]
 
-    spmm.build_cached = build_spmm
-    sddmm.build_cached = build_sddmm
+    spmm.build_cached, spmm.out_cache = build_spmm, cache_a
+    sddmm.build_cached, sddmm.out_cache = build_sddmm, cache_b
 
 
 if __name__ == "__main__":

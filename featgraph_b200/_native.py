@@ -17,6 +17,7 @@ ERROR_NAMES = {1: "invalid argument", 2: "CUDA error", 3: "out of device memory"
 SIGNATURES = {
     "fg_version": (ctypes.c_int, []),
     "fg_last_error": (ctypes.c_char_p, []),
+    "fg_kernel_signature": (ctypes.c_char_p, []),
     "fg_kernel_launch_count": (_i64, []),
     "fg_device_info": (ctypes.c_int, [_vp, _vp, _vp, _vp]),
     "fg_row_schedule_create": (ctypes.c_int, [_vp, _i64, _i32, _vp, _vp]),

@@ -25,6 +25,11 @@ int fail(int code, const char* fmt, ...);
 // Kernels launched by this library in this process (fg_kernel_launch_count).
 void count_launches(int n);
 
+// Compile-time shapes of the hot kernels of each source file, for fg_kernel_signature().
+const char* spmm_signature();
+const char* sddmm_signature();
+const char* sddmm_plan_signature();
+
 // SM count and L2 size of the current device, looked up once per device ordinal (a host thread may
 // move between devices; each device keeps its own figures).
 constexpr int kMaxDevices = 64;
@@ -54,9 +59,12 @@ __device__ __forceinline__ float4 ldg4(const float* p) {
     return __ldg(reinterpret_cast<const float4*>(p));
 }
 
-// L2 residency hints.  The kernels gather from a slice of the feature matrix that is sized to stay in
-// L2 while index arrays and outputs stream past it once per pass; without a hint the streams push
-// slice lines out.  Gathers therefore ask L2 to evict their lines last, streams to evict theirs first.
+// L2 residency hints, as build-time switches (both OFF by default).  The kernels gather from a slice of
+// the feature matrix that is sized to stay in L2 while index arrays and outputs stream past it once per
+// pass; the hints ask L2 to evict gathered lines last (FG_HINT_KEEP) and streamed lines first
+// (FG_HINT_STREAM).  Measured on B200 with the 233K-node graph they changed nothing that matters: SpMM was
+// 1-7 % slower with FG_HINT_KEEP (the policy operand costs an instruction slot per gather), SDDMM within
+// +-3 % either way - the slice's hit rate is set by its size against L2, not by the streams.
 #ifndef FG_HINT_KEEP
 #define FG_HINT_KEEP 0
 #endif

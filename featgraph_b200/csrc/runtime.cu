@@ -58,7 +58,17 @@ extern "C" {
 
 int64_t fg_kernel_launch_count(void) { return fg::g_launches.load(std::memory_order_relaxed); }
 
-int fg_version(void) { return 100; }
+int fg_version(void) { return 200; }
+
+const char* fg_kernel_signature(void) {
+    static char text[512] = {0};
+    static std::once_flag once;
+    std::call_once(once, [] {
+        snprintf(text, sizeof(text), "%s;%s;%s", fg::spmm_signature(), fg::sddmm_signature(),
+                 fg::sddmm_plan_signature());
+    });
+    return text;
+}
 
 const char* fg_last_error(void) { return fg::error_buffer(); }
 

@@ -424,6 +424,15 @@ int64_t l2_size_bytes() { return fg::device_props().l2_bytes; }
 
 }  // namespace
 
+#define FG_STR_(x) #x
+#define FG_STR(x) FG_STR_(x)
+const char* fg::sddmm_signature() {
+    // lane layout per tile width as G,NV,U,MINB for 32-, 64- and 128-float tiles; id prefetch depth
+    return "sddmm_tile<q8:" FG_STR(FG_Q8_G) "," FG_STR(FG_Q8_NV) "," FG_STR(FG_Q8_U) "," FG_STR(FG_Q8_MINB) "|q16:" FG_STR(
+        FG_Q16_G) "," FG_STR(FG_Q16_NV) "," FG_STR(FG_Q16_U) "," FG_STR(FG_Q16_MINB) "|q32:" FG_STR(FG_Q32_G) "," FG_STR(
+        FG_Q32_NV) "," FG_STR(FG_Q32_U) "," FG_STR(FG_Q32_MINB) "|pf" FG_STR(FG_SDDMM_PF) ">";
+}
+
 extern "C" {
 
 int fg_sddmm_coo_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src, int64_t ld_src,

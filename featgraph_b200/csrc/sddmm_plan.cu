@@ -280,6 +280,13 @@ int launch_colblock(const PlanArgs& a, bool masked, cudaStream_t s) {
 
 }  // namespace
 
+#define FG_STR_(x) #x
+#define FG_STR(x) FG_STR_(x)
+const char* fg::sddmm_plan_signature() {
+    // edges in flight per float4 count 1..4, blocks per SM
+    return "sddmm_colblock<u" FG_STR(FG_CB_U1) "," FG_STR(FG_CB_U2) "," FG_STR(FG_CB_U3) "," FG_STR(FG_CB_U4) "|2/SM>";
+}
+
 extern "C" {
 
 int32_t fg_sddmm_auto_partitions(int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d) {

@@ -38,6 +38,14 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// rows kernel shapes: gathers issued back to back per row and resident blocks per SM, regular / SHORT form
+#define FG_ROWS_CH 16
+#define FG_ROWS_MINB 2
+#define FG_SHORT_CH 4
+#define FG_SHORT_MINB 6
+#define FG_RING_SLOTS 3
+#define FG_RING_WARPS 4
+
 struct SpmmArgs {
     const int32_t* pos;    // indptr (CSR) or s1_pos (DDS: parts blocks of n_rows+1)
     const int32_t* idx;    // column ids (DDS: relative to the partition's first column)
@@ -104,8 +112,8 @@ struct Slice<1> {
 // SHORT: the form for rows of a few nonzeros, where what counts is how many rows an SM has in
 // flight, not how many gathers a row has: 4 gathers back to back and 6 blocks per SM.
 template <int G, int VEC, bool DDS, bool UNIT, bool SHORT>
-__global__ void __launch_bounds__(kThreads, SHORT ? 6 : 2) spmm_rows_kernel(const SpmmArgs a) {
-    constexpr int CHMAX = SHORT ? 4 : 16;
+__global__ void __launch_bounds__(kThreads, SHORT ? FG_SHORT_MINB : FG_ROWS_MINB) spmm_rows_kernel(const SpmmArgs a) {
+    constexpr int CHMAX = SHORT ? FG_SHORT_CH : FG_ROWS_CH;
     constexpr int CH = G < CHMAX ? G : CHMAX;  // gathers issued back to back
     const int lane = threadIdx.x & 31;
     const int lig = lane & (G - 1);
@@ -213,9 +221,9 @@ __global__ void __launch_bounds__(kThreads, SHORT ? 6 : 2) spmm_rows_kernel(cons
 // per warp, 16 resident warps per SM) measured faster than deeper rings with fewer warps: the
 // per-lane add chain needs the other warps to fill its 4-cycle gaps.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRingStages = 3;
+constexpr int kRingStages = FG_RING_SLOTS;
 constexpr int kRingNnz = 32;                 // nonzeros per slot
-constexpr int kLongWarps = 4;                // warps (= units) per block
+constexpr int kLongWarps = FG_RING_WARPS;    // warps (= units) per block
 constexpr int kLongThreads = kLongWarps * 32;
 constexpr int kSlotFloats = kRingNnz * 32 + kRingNnz;  // 32 slices of 32 floats + 32 values
 constexpr int kLongSmemBytes = kLongWarps * kRingStages * kSlotFloats * 4;
@@ -847,65 +855,86 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     const int cap = fg::pow2_ceil(d);
     if (tile > cap) tile = cap;
     if (tile < 4) tile = 4;
-    // Heavy and long rows first, through the shared-memory rings (CSR with a schedule only).
-    //
-    // When no slice of x can stay in L2 (graphs of millions of columns) those kernels run on a side
-    // stream, beside spmm_rows_kernel: their last rows - a few warps, each bound by its row's
-    // length (a 160,000-nonzero hub row takes 2.4 ms in the long-row kernel) - then finish under the
-    // other kernel instead of idling the GPU (R-MAT scale 22, d = 128: 7.5 -> 5.7 ms).  When a slice can stay resident
-    // the kernels run one after the other: side by side each would evict the slice the other one
-    // lives on (measured on the 233K-node graph: up to 25 % slower than in sequence).
-#ifdef FG_PROBE_SIDE_BY_SIDE_ONE_TILE
-    const bool side_by_side = !slice_can_stay_in_l2(n_cols) || d <= tile;
-#else
-    const bool side_by_side = !slice_can_stay_in_l2(n_cols);
-#endif
-    RowSplit split;
-    if (schedule && !dds) split = choose_row_split(*schedule, d, tile, side_by_side);
-    // Rows of fewer than 64 nonzeros (the schedule's first threshold) take the SHORT form of the
-    // rows kernel, launched last (in side-by-side mode on a stream of its own).
-    int64_t first_short = n_rows;
-    if (schedule && !dds) {
-        first_short = schedule->rows_at_least[0];
-        if (first_short < split.ring) first_short = split.ring;
-    }
+    // Heavy and long rows go through the shared-memory rings (CSR with a schedule only).  Where it pays,
+    // the kernels of a call run SIDE BY SIDE - heavy, long and short rows on three internal streams
+    // forked from and joined to the caller's - so that the last long rows, a few warps each bound by its
+    // row's length (a 20,000-nonzero row takes 0.15 ms even in the heavy-row kernel, a 160,000-nonzero hub
+    // row 2.4 ms in the long-row kernel), finish under the bulk of the work instead of idling the GPU:
+    //  * no slice of x can stay in L2 (millions of columns): always (R-MAT scale 22, d = 128: 7.5 -> 5.7 ms);
+    //  * a slice stays resident and the call is a single feature tile: all kernels gather from that one
+    //    slice (1/8 shard of the 233K-node graph: d = 32 0.225 -> 0.197 ms, d = 64 0.365 -> 0.320);
+    //  * a slice stays resident and the call walks several tiles: one after the other.  Side by side each
+    //    kernel walks its own tile sequence and evicts the slice the other one lives on; measured on that
+    //    shard at d = 512: in sequence 1.98 ms, whole call side by side 2.38 (2.95 with the split the
+    //    side-by-side model prefers; evict-first gathers in the ring kernels changed nothing), one fork /
+    //    join per tile 2.78 (each tile then pays the longest row's 0.15 ms and a drained GPU).
+    const bool resident = slice_can_stay_in_l2(n_cols);
     SideStream* side = side_stream();
-    const bool forked = side && side_by_side && (split.ring > 0 || first_short < n_rows) && side->fork_from(s);
-    auto stream_for = [&](int which) { return forked ? side->stream[which] : s; };
-    int rc = FG_OK;
-    {
-        SpmmArgs h = a;
-        h.n_tiles = (d + 31) / 32;
-        h.order_begin = 0;
-        h.n_sched = (int32_t)split.heavy;
-        rc = launch_heavy(h, split.wide, stream_for(SideStream::kHeavy));
-        if (rc == FG_OK) {
-            h.order_begin = (int32_t)split.heavy;
-            h.n_sched = (int32_t)(split.ring - split.heavy);
-            rc = launch_long(h, stream_for(SideStream::kRing));
+    // the kernels of one launch on feature columns [c0, c0 + w)
+    auto columns = [&](int c0, int w, const RowSplit& split, bool beside) -> int {
+        // Rows of fewer than 64 nonzeros (the schedule's first threshold) take the SHORT form of the
+        // rows kernel, launched last (beside the others on a stream of its own).
+        int64_t first_short = n_rows;
+        if (schedule && !dds) {
+            first_short = schedule->rows_at_least[0];
+            if (first_short < split.ring) first_short = split.ring;
         }
-    }
-    a.n_tiles = (d + tile - 1) / tile;
-    if (rc == FG_OK) {
-        a.order_begin = (int32_t)split.ring;
-        a.n_sched = (int32_t)(first_short - split.ring);
-        rc = launch_tile<false>(a, tile, dds, s);
-    }
-    if (rc == FG_OK && first_short < n_rows) {
-        a.order_begin = (int32_t)first_short;
-        a.n_sched = (int32_t)(n_rows - first_short);
-        rc = launch_tile<true>(a, tile, dds, stream_for(SideStream::kShort));
-    }
-    // join even after a failed launch: the side streams must come back to the caller's stream (a
-    // capture could not end otherwise); work enqueued on it afterwards waits for all kernels
-    if (forked) {
-        const int rcj = side->join_to(s);
-        if (rc == FG_OK) rc = rcj;
-    }
-    return rc;
+        const bool forked = beside && side && (split.ring > 0 || first_short < n_rows) && side->fork_from(s);
+        auto stream_for = [&](int which) { return forked ? side->stream[which] : s; };
+        SpmmArgs h = a;
+        h.x = a.x + c0;
+        h.out = a.out + c0;
+        h.d = w;
+        int rc = FG_OK;
+        {
+            SpmmArgs r = h;
+            r.n_tiles = (w + 31) / 32;
+            r.order_begin = 0;
+            r.n_sched = (int32_t)split.heavy;
+            rc = launch_heavy(r, split.wide, stream_for(SideStream::kHeavy));
+            if (rc == FG_OK) {
+                r.order_begin = (int32_t)split.heavy;
+                r.n_sched = (int32_t)(split.ring - split.heavy);
+                rc = launch_long(r, stream_for(SideStream::kRing));
+            }
+        }
+        h.n_tiles = (w + tile - 1) / tile;
+        if (rc == FG_OK) {
+            h.order_begin = (int32_t)split.ring;
+            h.n_sched = (int32_t)(first_short - split.ring);
+            rc = launch_tile<false>(h, tile, dds, s);
+        }
+        if (rc == FG_OK && first_short < n_rows) {
+            h.order_begin = (int32_t)first_short;
+            h.n_sched = (int32_t)(n_rows - first_short);
+            rc = launch_tile<true>(h, tile, dds, stream_for(SideStream::kShort));
+        }
+        // join even after a failed launch: the side streams must come back to the caller's stream (a
+        // capture could not end otherwise); work enqueued on it afterwards waits for all kernels
+        if (forked) {
+            const int rcj = side->join_to(s);
+            if (rc == FG_OK) rc = rcj;
+        }
+        return rc;
+    };
+    const RowSplit none;
+    if (!schedule || dds) return columns(0, d, none, false);
+    if (!resident) return columns(0, d, choose_row_split(*schedule, d, tile, true), true);
+    if (d <= tile) return columns(0, d, choose_row_split(*schedule, d, tile, true), true);
+    return columns(0, d, choose_row_split(*schedule, d, tile, false), false);
 }
 
 }  // namespace
+
+#define FG_STR_(x) #x
+#define FG_STR(x) FG_STR_(x)
+const char* fg::spmm_signature() {
+    // rows kernel: gathers in flight, blocks per SM (regular / short form); ring: slots x nonzeros, warps;
+    // heavy: warps (narrow|wide), turns deep
+    return "spmm_rows<ch" FG_STR(FG_ROWS_CH) "," FG_STR(FG_ROWS_MINB) "/SM|short:ch" FG_STR(FG_SHORT_CH) "," FG_STR(
+        FG_SHORT_MINB) "/SM>,ring<" FG_STR(FG_RING_SLOTS) "x32," FG_STR(FG_RING_WARPS) "w>,heavy<4|8w,3deep>,hints<" FG_STR(
+        FG_HINT_KEEP) FG_STR(FG_HINT_STREAM) ">";
+}
 
 extern "C" {
 

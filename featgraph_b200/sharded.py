@@ -137,6 +137,55 @@ def remap_columns(adj_csr, bounds):
     return remap_columns_to_padded(adj_csr, bounds) if use_padded_layout(bounds) else adj_csr
 
 
+# ---- host-buffer steps -------------------------------------------------------------------------------
+# The single-GPU modules pipeline host copies inside one call (run_host -> fg_*_host).  A sharded call has
+# the exchange between copy-in and kernel, so here the three stages are spread over streams of this
+# layer: copy-in (host -> this rank's rows on the device, then the exchange behind it), the caller's
+# compute stream (kernels), copy-out (results -> host).  Calls only enqueue; ``host_sync`` waits.  With
+# the next call's copy-in and exchange issued before the current call's kernels, a step costs about
+# max(copies in, kernels, copies out) instead of their sum.
+_copy_streams = {}
+
+
+def copy_streams(device):
+    """(copy-in, copy-out) streams of this layer on ``device`` (created once per device)."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _copy_streams:
+        _copy_streams[key] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+    return _copy_streams[key]
+
+
+def host_sync(device):
+    """Wait until every host-buffer call issued so far on ``device`` has delivered its result."""
+    s_in, s_out = copy_streams(device)
+    s_in.synchronize()
+    torch.cuda.current_stream(device).synchronize()
+    s_out.synchronize()
+
+
+def copy_out_async(result, out_host, device, holder):
+    """Enqueue ``out_host <- result`` on the copy-out stream behind what the compute stream holds now.
+    The event of the copy is kept on ``holder`` under the result buffer's address: the next kernel that
+    overwrites that buffer waits for it (``wait_for_copy_out``)."""
+    _, s_out = copy_streams(device)
+    done = torch.cuda.current_stream(device).record_event()
+    s_out.wait_event(done)
+    with torch.cuda.stream(s_out):
+        out_host.copy_(result, non_blocking=True)
+        holder.__dict__.setdefault("_out_done", {})[result.data_ptr()] = s_out.record_event()
+    return out_host
+
+
+def wait_for_copy_out(buffer, device, holder):
+    """Make the compute stream wait until the last copy-out of ``buffer`` (if any) has left the device."""
+    if buffer is None:
+        return
+    ev = holder.__dict__.get("_out_done", {}).pop(buffer.data_ptr(), None)
+    if ev is not None:
+        torch.cuda.current_stream(device).wait_event(ev)
+
+
 class _ShardedBase:
     def __init__(self, bounds, group, device):
         self.group = group
@@ -181,10 +230,12 @@ class GatheredFeatures(_ShardedBase):
         super().__init__(bounds, group, device)
         self.feat_len = int(feat_len)
         self.full = torch.zeros((self.n, self.feat_len), dtype=torch.float32, device=device)
+        self._own_full = True
 
     def gather(self, x_local):
         if self.world == 1:
             self.full = x_local  # nothing to exchange: the local rows are all rows
+            self._own_full = False
         else:
             self._gather(self.full, x_local)
         return self
@@ -200,8 +251,73 @@ class GatheredFeatures(_ShardedBase):
         self._work = self._gather_async(self.full, x_local)
         return self
 
+    def gather_from_host_async(self, x_host_local):
+        """``gather_async`` for rows that live in (pinned) host memory: the copy to the device runs on this
+        layer's copy-in stream and the exchange starts behind it, neither touching the compute stream
+        until ``wait()``.  A call may be issued while earlier kernels still read this buffer's previous
+        contents only if those kernels were enqueued through ``ShardedSpMM.run_host`` /
+        ``ShardedSDDMM.run_host`` (they leave the event this call waits for)."""
+        s_in, _ = copy_streams(self.device)
+        rows = self.row_hi - self.row_lo
+        if tuple(x_host_local.shape) != (rows, self.feat_len):
+            raise ValueError("local block has shape %s, this rank owns %d rows of %d columns"
+                             % (tuple(x_host_local.shape), rows, self.feat_len))
+        self._work = None
+        read_done = getattr(self, "_read_done", None)
+        if read_done is not None:
+            s_in.wait_event(read_done)  # the kernels that gathered from the previous contents
+        with torch.cuda.stream(s_in):
+            if self.world == 1:
+                if self.full is None or tuple(self.full.shape) != (rows, self.feat_len) or not self._own_full:
+                    self.full = torch.empty((rows, self.feat_len), dtype=torch.float32, device=self.device)
+                    self._own_full = True
+                self.full.copy_(x_host_local, non_blocking=True)
+                self._copied = s_in.record_event()
+                return self
+            if self.padded:
+                mine = self.full[self.rank * self.slot:(self.rank + 1) * self.slot]
+                mine[:rows].copy_(x_host_local, non_blocking=True)
+                local = mine[:rows]
+            else:
+                local = self.full[self.row_lo:self.row_hi]
+                local.copy_(x_host_local, non_blocking=True)
+            if dist.get_backend(self.group) != "nccl":
+                s_in.synchronize()
+                self._gather_in_place(local)
+                return self
+            try:
+                # the collective is ordered behind the copy: it is issued with the copy-in stream current
+                if self.padded:
+                    self._work = dist.all_gather_into_tensor(self.full, mine, group=self.group, async_op=True)
+                else:
+                    views = [self.full[int(self.bounds[p]):int(self.bounds[p + 1])] for p in range(self.world)]
+                    self._work = dist.all_gather(views, local, group=self.group, async_op=True)
+            except Exception as exc:
+                raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (self.rank, self.world, exc)) from exc
+        return self
+
+    def _gather_in_place(self, local):
+        """Backends without stream semantics (gloo): the blocking exchange, this rank's rows already in place."""
+        try:
+            if self.padded:
+                mine = self.full[self.rank * self.slot:(self.rank + 1) * self.slot]
+                dist.all_gather([self.full[p * self.slot:(p + 1) * self.slot] for p in range(self.world)],
+                                mine.clone(), group=self.group)
+            else:
+                for p in range(self.world):
+                    v = self.full[int(self.bounds[p]):int(self.bounds[p + 1])]
+                    if v.numel():
+                        dist.broadcast(v, src=dist.get_global_rank(self.group, p) if self.group is not None else p,
+                                       group=self.group)
+        except Exception as exc:
+            raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (self.rank, self.world, exc)) from exc
+
     def wait(self):
         """Make the current stream wait for the exchange started by ``gather_async``."""
+        copied = getattr(self, "_copied", None)
+        if copied is not None:  # world size 1: only the host copy to wait for
+            torch.cuda.current_stream(self.device).wait_event(copied)
+            self._copied = None
         work = getattr(self, "_work", None)
         if work is not None:
             try:
@@ -253,6 +369,17 @@ class ShardedSpMM(_ShardedBase):
         return self.compute()
 
 
+    def run_host(self, gathered, out_host):
+        """Host-result call: the kernel on ``gathered`` (a ``GatheredFeatures`` whose exchange was started by
+        ``gather_from_host_async`` or ``gather_async``), then this rank's rows of A.X copied to the pinned
+        host tensor ``out_host`` on the copy-out stream.  Only enqueues; ``sharded.host_sync(device)`` waits."""
+        gathered.wait()
+        wait_for_copy_out(self.module.out, self.device, self)  # the previous result has left the device
+        out = self.module.run([gathered.full])
+        gathered._read_done = torch.cuda.current_stream(self.device).record_event()
+        return copy_out_async(out, out_host, self.device, self)
+
+
 class ShardedSDDMM(_ShardedBase):
     """Edge-sharded SDDMM by the same row ranges (square adjacency)."""
 
@@ -286,3 +413,28 @@ class ShardedSDDMM(_ShardedBase):
             return self.module.run([src_local.full, dst_local])
         self.gather(src_local)
         return self.compute(dst_local)
+
+    def run_host(self, gathered, dst_host_local, out_host):
+        """Host-buffer call: ``gathered`` as in ``ShardedSpMM.run_host``; this rank's rows of the row-side
+        matrix come from the (pinned) host tensor ``dst_host_local`` over the copy-in stream, the per-edge
+        result goes to ``out_host`` over the copy-out stream.  Only enqueues; ``sharded.host_sync`` waits."""
+        s_in, _ = copy_streams(self.device)
+        stream = torch.cuda.current_stream(self.device)
+        rows = self.row_hi - self.row_lo
+        d = gathered.feat_len
+        stages = self.__dict__.setdefault("_dst_stages", {})  # one staging buffer per feature length
+        if d not in stages:
+            stages[d] = [torch.empty((rows, d), dtype=torch.float32, device=self.device), None]
+        stage, last_read = stages[d]
+        if last_read is not None:
+            s_in.wait_event(last_read)  # the kernel that read the staging buffer last
+        with torch.cuda.stream(s_in):
+            stage.copy_(dst_host_local, non_blocking=True)
+            copied = s_in.record_event()
+        gathered.wait()
+        stream.wait_event(copied)
+        wait_for_copy_out(self.module.out, self.device, self)
+        out = self.module.run([gathered.full, stage])
+        stages[d][1] = stream.record_event()
+        gathered._read_done = stages[d][1]
+        return copy_out_async(out, out_host, self.device, self)

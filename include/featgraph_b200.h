@@ -47,6 +47,12 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch). */
 int fg_version(void);
 
+/* Compile-time shapes of the hot kernels in this build (lane layouts, gathers in flight, ring depths) as
+ * one short string.  Measurements that were taken from one build of the kernels (profiler counters kept
+ * beside a benchmark) carry this string, so that a reader can tell whether they still describe the
+ * kernels that ran.  No counterpart in the reference (its kernels are generated per call). */
+const char* fg_kernel_signature(void);
+
 /* Text of the last error raised on the calling thread ("" if none). Never NULL. */
 const char* fg_last_error(void);
 

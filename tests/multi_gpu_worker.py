@@ -74,6 +74,21 @@ def check_graph(graph, rank, world, device):
         np.testing.assert_array_equal(spmm.run(g2.wait()).cpu().numpy(), want)
         want_e = oracle.sddmm(coo.row, coo.col, x, y)[adj.indptr[lo]:adj.indptr[hi]]
         np.testing.assert_allclose(e, want_e, rtol=1e-5, atol=1e-4)
+        # host-buffer step: rows come from pinned host memory, results go back to it (twice: buffers reused)
+        from featgraph_b200 import sharded
+        xh, yh = torch.from_numpy(x[lo:hi].copy()).pin_memory(), torch.from_numpy(y[lo:hi].copy()).pin_memory()
+        oh = torch.empty((hi - lo, d)).pin_memory()
+        eh = torch.empty((len(want_e),)).pin_memory()
+        g3 = GatheredFeatures(bounds, d, device=device)
+        for _ in range(2):
+            oh.zero_()
+            eh.zero_()
+            g3.gather_from_host_async(xh)
+            spmm.run_host(g3, oh)
+            sddmm.run_host(g3, yh, eh)
+            sharded.host_sync(device)
+            np.testing.assert_array_equal(oh.numpy(), want)
+            np.testing.assert_array_equal(eh.numpy(), e)
     assert spmm.padded == (graph == "power-law"), (graph, bounds)
 
 
