@@ -26,6 +26,8 @@ SIGNATURES = {
     "fg_row_schedule_rows_at_least": (_i64, [_vp, _i64]),
     "fg_row_schedule_destroy": (None, [_vp]),
     "fg_spmm_csr_f32": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "fg_spmm_sddmm_fused_f32": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64,
+                                               _i32, _vp]),
     "fg_spmm_csr_f32_static": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fg_spmm_dds_f32": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "fg_sddmm_coo_f32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp]),

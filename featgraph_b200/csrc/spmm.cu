@@ -924,6 +924,363 @@ int spmm_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int
     return columns(0, d, choose_row_split(*schedule, d, tile, false), false);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Aggregate, then score, in one pass over the rows (one GCN-style layer step):
+//     H = A . X                         as fg_spmm_csr_f32 (sequential sums, the same bits)
+//     out[e] = dot(H[row e], Y[col e])  as fg_sddmm_coo_f32 on the CSR-ordered edge list
+// which a caller of the reference runs as two built functions back to back
+// (python/featgraph/module/spmm.py:142-161, then python/featgraph/module/sddmm.py:115-129).
+//
+// A group of G lanes owns a row, as in spmm_rows_kernel, and all d columns of it (d <= 4 G): when the
+// row's sum is finished its slice of H is in the lanes' registers, so the same group walks the row's
+// nonzeros a second time, gathers the slices of y and reduces each edge's dot product with the
+// transposed butterfly of the SDDMM kernels.  Against two calls this saves reading H back (once per
+// row), the second kernel's pass over the row ids, and a kernel's tail; H is still written (a layer
+// needs it).  Rows too long for one group (the launch's long / heavy rows) take the ring kernels for
+// H and score_long_rows_kernel for their edges.
+// ---------------------------------------------------------------------------------------------
+struct FusedArgs {
+    SpmmArgs a;        // a.out = H
+    const float* y;    // [n_cols, d], row stride ldy
+    int64_t ldy;
+    float* edge_out;   // [nnz], CSR order
+};
+
+__device__ __forceinline__ float dot4f(float acc, const float4& p, const float4& q) {
+    acc = fmaf(p.x, q.x, acc);
+    acc = fmaf(p.y, q.y, acc);
+    acc = fmaf(p.z, q.z, acc);
+    acc = fmaf(p.w, q.w, acc);
+    return acc;
+}
+
+// Transposed butterfly over the G lanes of a group.  In: pc[j] = this lane's partial dot product of
+// chunk edge j (U edges).  Out (after the in-chunk steps): pc[0] = for the edge picked by the lane's low
+// log2(U) bits, the sum over the lanes that differ from it in those bits.
+template <int U>
+__device__ __forceinline__ float butterfly_in_chunk(float (&pc)[U], int lig) {
+#pragma unroll
+    for (int o = 1; o < U; o <<= 1) {
+        const bool upper = (lig & o) != 0;
+#pragma unroll
+        for (int i = 0; i < U / (2 * o); ++i) {
+            const float send = upper ? pc[2 * i] : pc[2 * i + 1];
+            const float keep = upper ? pc[2 * i + 1] : pc[2 * i];
+            pc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+    }
+    return pc[0];
+}
+// The remaining steps across the G / U chunks: afterwards r[0] on lane i of the group is edge i's total.
+template <int G, int U>
+__device__ __forceinline__ float butterfly_across_chunks(float (&r)[G / U], int lig) {
+#pragma unroll
+    for (int o = U; o < G; o <<= 1) {
+        const bool upper = (lig & o) != 0;
+        const int h = o / U;
+#pragma unroll
+        for (int i = 0; i < G / U / (2 * h); ++i) {
+            const float send = upper ? r[2 * i] : r[2 * i + 1];
+            const float keep = upper ? r[2 * i + 1] : r[2 * i];
+            r[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+    }
+    return r[0];
+}
+
+// G lanes x 4 floats cover all d columns (one feature tile).  SHORT as in spmm_rows_kernel.
+template <int G, bool UNIT, bool SHORT>
+__global__ void __launch_bounds__(kThreads, SHORT ? FG_SHORT_MINB : FG_ROWS_MINB) fused_rows_kernel(const FusedArgs f) {
+    const SpmmArgs& a = f.a;
+    constexpr int CHMAX = SHORT ? FG_SHORT_CH : FG_ROWS_CH;
+    constexpr int CH = G < CHMAX ? G : CHMAX;
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (G - 1);
+    const int64_t unit = (int64_t)blockIdx.x * (kThreads / G) + (threadIdx.x / G);
+    const bool live = unit < a.n_sched;
+    int row = 0;
+    int2 extent = make_int2(0, 0);
+    if (live) {
+        const int p = a.order_begin + (int)unit;
+        row = a.order ? a.order[p] : p;
+        if (a.extent) {
+            extent = a.extent[p];
+        } else {
+            extent.x = a.pos[row];
+            extent.y = a.pos[row + 1] - extent.x;
+        }
+    }
+    const int col = lig * 4;
+    const bool col_ok = live && col < a.d;
+    const float* xcol = a.x + (col_ok ? col : 0);  // idle lanes read (and discard) column 0
+    const float* ycol = f.y + (col_ok ? col : 0);
+    const int ldx32 = (int)a.ldx, ldy32 = (int)f.ldy;
+    const uint64_t keep_policy = fg::l2_keep_policy();
+    const int start = extent.x, len = extent.y;
+    const int max_len = __reduce_max_sync(0xffffffffu, len);  // every lane of the warp runs the same batches
+
+    // ---- aggregate: the loop of spmm_rows_kernel ----
+    Slice<4> acc;
+    acc.zero();
+    {
+        int my_c = -1;
+        float my_v = 0.f;
+        if (lig < len) {
+            my_c = fg::ld_stream(a.idx + start + lig);
+            if (!UNIT) my_v = fg::ld_stream(a.vals + start + lig);
+        }
+        for (int base = 0; base < max_len; base += G) {
+            int nx_c = -1;
+            float nx_v = 0.f;
+            if (base + G + lig < len) {
+                nx_c = fg::ld_stream(a.idx + start + base + G + lig);
+                if (!UNIT) nx_v = fg::ld_stream(a.vals + start + base + G + lig);
+            }
+#pragma unroll
+            for (int j0 = 0; j0 < G; j0 += CH) {
+                if (base + j0 >= max_len) break;  // warp-uniform
+                int c[CH];
+                float v[CH];
+                Slice<4> xr[CH];
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    c[j] = __shfl_sync(0xffffffffu, my_c, j0 + j, G);
+                    v[j] = UNIT ? 1.f : __shfl_sync(0xffffffffu, my_v, j0 + j, G);
+                }
+#pragma unroll
+                for (int j = 0; j < CH; ++j) xr[j].load(xcol + (int64_t)(c[j] < 0 ? 0 : c[j]) * ldx32, keep_policy);
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    Slice<4> next = acc;
+                    if (UNIT)
+                        next.add(xr[j]);
+                    else
+                        next.axpy(v[j], xr[j]);
+                    acc.select(c[j] >= 0, next);
+                }
+            }
+            my_c = nx_c;
+            my_v = nx_v;
+        }
+    }
+    if (col_ok) acc.store(a.out + (int64_t)row * a.ldo + col);
+    if (!col_ok) acc.zero();  // lanes beyond the row's width add nothing to a dot product
+
+    // ---- score: the same nonzeros again (their ids are still in L1 / L2), against y ----
+    {
+        int my_c = -1;
+        if (lig < len) my_c = a.idx[start + lig];
+        for (int base = 0; base < max_len; base += G) {
+            int nx_c = -1;
+            if (base + G + lig < len) nx_c = a.idx[start + base + G + lig];
+            float r[G / CH];
+#pragma unroll
+            for (int j0 = 0; j0 < G; j0 += CH) {
+                if (base + j0 >= max_len) {  // warp-uniform
+                    r[j0 / CH] = 0.f;
+                    continue;
+                }
+                int c[CH];
+                float pc[CH];
+                Slice<4> yr[CH];
+#pragma unroll
+                for (int j = 0; j < CH; ++j) c[j] = __shfl_sync(0xffffffffu, my_c, j0 + j, G);
+#pragma unroll
+                for (int j = 0; j < CH; ++j) yr[j].load(ycol + (int64_t)(c[j] < 0 ? 0 : c[j]) * ldy32, keep_policy);
+#pragma unroll
+                for (int j = 0; j < CH; ++j) pc[j] = dot4f(0.f, acc.v, yr[j].v);
+                r[j0 / CH] = butterfly_in_chunk<CH>(pc, lig);
+            }
+            const float total = butterfly_across_chunks<G, CH>(r, lig);
+            if (base + lig < len) fg::st_stream(f.edge_out + start + base + lig, total);
+            my_c = nx_c;
+        }
+    }
+}
+
+// Edges of the long rows (order[0, n_sched)): H is in memory (written by the ring kernels).  A block takes
+// (row, share); its warps stride over the row's 32-edge batches, each lane holding one float4 of H[row]
+// and of the gathered y rows (d <= 128), with the whole-warp butterfly of the column-block SDDMM kernel.
+constexpr int kScoreShares = 8;
+__global__ void __launch_bounds__(kThreads, 2) score_long_rows_kernel(const FusedArgs f) {
+    const SpmmArgs& a = f.a;
+    constexpr int U = 16;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int row = a.order[a.order_begin + blockIdx.x];
+    const int start = a.pos[row];
+    const int len = a.pos[row + 1] - start;
+    const int n_batches = (len + 31) / 32;
+    const int col = lane * 4;
+    const bool col_ok = col < a.d;
+    float4 h = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col_ok) h = *reinterpret_cast<const float4*>(a.out + (int64_t)row * a.ldo + col);
+    const float* ycol = f.y + (col_ok ? col : 0);
+    const int ldy32 = (int)f.ldy;
+    const uint64_t keep_policy = fg::l2_keep_policy();
+    for (int b = blockIdx.y * (kThreads / 32) + warp; b < n_batches; b += gridDim.y * (kThreads / 32)) {
+        const int e0 = start + 32 * b;
+        const int cnt = min(32, len - 32 * b);
+        int c_l = 0;  // lanes past the end gather row 0 of y; their products are never stored
+        if (lane < cnt) c_l = fg::ld_stream(a.idx + e0 + lane);
+        float r[32 / U];
+#pragma unroll
+        for (int s = 0; s < 32; s += U) {
+            if (s >= cnt) {  // warp-uniform
+                r[s / U] = 0.f;
+                continue;
+            }
+            int c[U];
+            float pc[U];
+            float4 yr[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) c[u] = __shfl_sync(0xffffffffu, c_l, s + u);
+#pragma unroll
+            for (int u = 0; u < U; ++u) yr[u] = fg::ldg4_keep(ycol + (int64_t)c[u] * ldy32, keep_policy);
+#pragma unroll
+            for (int u = 0; u < U; ++u) pc[u] = col_ok ? dot4f(0.f, h, yr[u]) : 0.f;
+            r[s / U] = butterfly_in_chunk<U>(pc, lane);
+        }
+        const float total = butterfly_across_chunks<32, U>(r, lane);
+        if (lane < cnt) fg::st_stream(f.edge_out + e0 + lane, total);
+    }
+}
+
+template <int G, bool SHORT>
+int launch_fused(const FusedArgs& f, cudaStream_t s) {
+    const int64_t units_per_block = kThreads / G;
+    const int64_t blocks = (f.a.n_sched + units_per_block - 1) / units_per_block;
+    if (blocks > 0x7fffffffLL) return fg::fail(FG_ERR_INVALID_ARGUMENT, "grid too large");
+    if (blocks == 0) return FG_OK;
+    if (f.a.vals == nullptr)
+        fused_rows_kernel<G, true, SHORT><<<(unsigned)blocks, kThreads, 0, s>>>(f);
+    else
+        fused_rows_kernel<G, false, SHORT><<<(unsigned)blocks, kThreads, 0, s>>>(f);
+    FG_CUDA_TRY(cudaGetLastError());
+    fg::count_launches(1);
+    return FG_OK;
+}
+
+template <bool SHORT>
+int launch_fused_width(const FusedArgs& f, int lanes, cudaStream_t s) {
+    switch (lanes) {
+        case 1: return launch_fused<1, SHORT>(f, s);
+        case 2: return launch_fused<2, SHORT>(f, s);
+        case 4: return launch_fused<4, SHORT>(f, s);
+        case 8: return launch_fused<8, SHORT>(f, s);
+        case 16: return launch_fused<16, SHORT>(f, s);
+        default: return launch_fused<32, SHORT>(f, s);
+    }
+}
+
+int fused_dispatch(const fg_row_schedule* schedule, const int32_t* pos, const int32_t* idx, const float* vals,
+                   const float* x, int64_t ldx, const float* y, int64_t ldy, float* h, int64_t ldh, float* edge_out,
+                   int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d, void* stream) {
+    if (n_rows < 0 || n_cols < 0 || nnz < 0 || d < 1)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d", (long long)n_rows,
+                        (long long)n_cols, (long long)nnz, d);
+    if (n_rows > INT32_MAX || n_cols > INT32_MAX || nnz > INT32_MAX)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "sizes beyond int32 indexing are not supported");
+    if (d > 128 || d % 4 != 0)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT,
+                        "d=%d: the fused call keeps a whole row of H in one group's registers and takes d <= 128, "
+                        "a multiple of 4 (use fg_spmm_csr_f32 + fg_sddmm_coo_f32 otherwise)", d);
+    if (ldx == 0) ldx = d;
+    if (ldy == 0) ldy = d;
+    if (ldh == 0) ldh = d;
+    if (ldx < d || ldy < d || ldh < d || ldx > INT32_MAX || ldy > INT32_MAX || ldh > INT32_MAX || (ldx % 4) || (ldy % 4) ||
+        (ldh % 4))
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row strides must be 0 or multiples of 4 in [d=%d, 2^31)", d);
+    if (n_rows == 0) return FG_OK;
+    if (!pos || !h) return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL position or output array");
+    if (nnz > 0 && (!idx || !x || !y || !edge_out)) return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL array argument");
+    if (!fg::aligned16(x) || !fg::aligned16(y) || !fg::aligned16(h))
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "the fused call needs 16-byte aligned feature matrices");
+    if (schedule && fg_row_schedule_num_rows(schedule) != n_rows)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "row schedule was built for %lld rows, not %lld",
+                        (long long)fg_row_schedule_num_rows(schedule), (long long)n_rows);
+    if (schedule && schedule->d_extent && schedule->nnz != nnz)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT,
+                        "row schedule was built from an adjacency of %lld nonzeros, this call has %lld: rebuild the "
+                        "schedule when the adjacency changes", (long long)schedule->nnz, (long long)nnz);
+    FusedArgs f;
+    SpmmArgs& a = f.a;
+    a.pos = pos;
+    a.idx = idx;
+    a.vals = vals;
+    a.x = x;
+    a.out = h;
+    a.order = schedule ? fg_row_schedule_order(schedule) : nullptr;
+    a.extent = schedule ? schedule->d_extent : nullptr;
+    a.order_begin = 0;
+    a.n_sched = (int32_t)n_rows;
+    a.n_rows = (int32_t)n_rows;
+    a.d = d;
+    a.ldx = ldx;
+    a.ldo = ldh;
+    a.n_tiles = 1;
+    a.parts = 1;
+    a.cols_per_part = 0;
+    f.y = y;
+    f.ldy = ldy;
+    f.edge_out = edge_out;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int lanes = fg::pow2_ceil(d) / 4;  // G: lanes per row
+    // Long rows: the split a side-by-side SpMM launch would choose (their sums need the rings whatever
+    // follows); their edges are scored afterwards from H in memory.
+    RowSplit split;
+    int64_t first_short = n_rows;
+    if (schedule) {
+        split = choose_row_split(*schedule, d, fg::pow2_ceil(d), true);
+        first_short = schedule->rows_at_least[0];
+        if (first_short < split.ring) first_short = split.ring;
+    }
+    SideStream* side = side_stream();
+    const bool forked = side && (split.ring > 0 || first_short < n_rows) && side->fork_from(s);
+    auto stream_for = [&](int which) { return forked ? side->stream[which] : s; };
+    int rc = FG_OK;
+    if (split.ring > 0) {
+        // heavy rows, long rows and then their edges, one after the other on one stream
+        cudaStream_t ls = stream_for(SideStream::kHeavy);
+        SpmmArgs r = a;
+        r.n_tiles = (d + 31) / 32;
+        r.order_begin = 0;
+        r.n_sched = (int32_t)split.heavy;
+        rc = launch_heavy(r, split.wide, ls);
+        if (rc == FG_OK) {
+            r.order_begin = (int32_t)split.heavy;
+            r.n_sched = (int32_t)(split.ring - split.heavy);
+            rc = launch_long(r, ls);
+        }
+        if (rc == FG_OK) {
+            FusedArgs g = f;
+            g.a.order_begin = 0;
+            g.a.n_sched = (int32_t)split.ring;
+            score_long_rows_kernel<<<dim3((unsigned)split.ring, kScoreShares), kThreads, 0, ls>>>(g);
+            const cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) rc = fg::fail(FG_ERR_CUDA, "score_long_rows_kernel: %s", cudaGetErrorString(e));
+            fg::count_launches(1);
+        }
+    }
+    if (rc == FG_OK) {
+        FusedArgs g = f;
+        g.a.order_begin = (int32_t)split.ring;
+        g.a.n_sched = (int32_t)(first_short - split.ring);
+        rc = launch_fused_width<false>(g, lanes, s);
+    }
+    if (rc == FG_OK && first_short < n_rows) {
+        FusedArgs g = f;
+        g.a.order_begin = (int32_t)first_short;
+        g.a.n_sched = (int32_t)(n_rows - first_short);
+        rc = launch_fused_width<true>(g, lanes, stream_for(SideStream::kShort));
+    }
+    if (forked) {
+        const int rcj = side->join_to(s);
+        if (rc == FG_OK) rc = rcj;
+    }
+    return rc;
+}
+
 }  // namespace
 
 #define FG_STR_(x) #x
@@ -944,6 +1301,14 @@ int fg_spmm_csr_f32(const fg_row_schedule* schedule, const int32_t* d_indptr,
                     int32_t feat_tile, void* stream) {
     return spmm_dispatch(schedule, d_indptr, d_indices, d_vals, d_x, ldx, d_out, ldo, n_rows, n_cols,
                          nnz, d, 1, feat_tile, stream, false);
+}
+
+int fg_spmm_sddmm_fused_f32(const fg_row_schedule* schedule, const int32_t* d_indptr, const int32_t* d_indices,
+                            const float* d_vals, const float* d_x, int64_t ldx, const float* d_y, int64_t ldy,
+                            float* d_h, int64_t ldh, float* d_edge_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                            int32_t d, void* stream) {
+    return fused_dispatch(schedule, d_indptr, d_indices, d_vals, d_x, ldx, d_y, ldy, d_h, ldh, d_edge_out, n_rows,
+                          n_cols, nnz, d, stream);
 }
 
 int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,

@@ -141,6 +141,24 @@ int fg_spmm_dds_f32(const fg_row_schedule* schedule, const int32_t* d_s1_pos,
                     int32_t num_col_partitions, int32_t feat_tile, void* stream);
 
 /* --------------------------------------------------------------------------------------
+ * Aggregate, then score, in one pass over the rows (one GCN-style layer step):
+ *     h = A . x                              the values (bits) of fg_spmm_csr_f32
+ *     edge_out[e] = dot(h[row e], y[col e])  for the nonzeros in CSR order, as fg_sddmm_coo_f32 sums it
+ * It replaces the two built functions a caller of the reference runs back to back for this step
+ * (python/featgraph/module/spmm.py:159-160, then python/featgraph/module/sddmm.py:128 with the SpMM output
+ * as the row-side input).  The lanes that have just finished a row of h still hold it in registers and
+ * score the row's edges at once: h is not read back, the row ids are not walked a second time.
+ * x, y: [n_cols, d]; h: [n_rows, d] (always written); edge_out: [nnz].  d <= 128 and a multiple of 4, all
+ * matrices 16-byte aligned with strides that are multiples of 4 (0 = d).  d_vals may be NULL (all ones).
+ * With a schedule (built from this d_indptr) long rows take the ring kernels for h and a kernel of their
+ * own for their edges, on internal streams forked from and joined to `stream` as in fg_spmm_csr_f32.
+ * -------------------------------------------------------------------------------------- */
+int fg_spmm_sddmm_fused_f32(const fg_row_schedule* schedule, const int32_t* d_indptr, const int32_t* d_indices,
+                            const float* d_vals, const float* d_x, int64_t ldx, const float* d_y, int64_t ldy,
+                            float* d_h, int64_t ldh, float* d_edge_out, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                            int32_t d, void* stream);
+
+/* --------------------------------------------------------------------------------------
  * SpMM, CSR, without any device allocation (no counterpart in the reference; it exists for
  * callers that cannot tolerate a cudaMalloc - a process whose own pool already owns all device
  * memory, or a latency-critical loop that must not hit the device-wide synchronisation an
