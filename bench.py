@@ -72,6 +72,11 @@ def parse_args():
     p.add_argument("--no-prefetch", action="store_true",
                    help="N > 1: exchange each feature matrix right before its ops instead of during the previous ones")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--all-gather", action="store_true",
+                   help="C4 at N > 1: exchange whole feature matrices (all-gather) even where exchanging only the rows "
+                        "each shard references would be chosen")
+    p.add_argument("--fused", action="store_true",
+                   help="C4 on one GPU: the fused aggregate-then-score call instead of SpMM followed by SDDMM")
     p.add_argument("--e2e-steps", type=int, default=2)
     return p.parse_args()
 
@@ -338,8 +343,23 @@ def run_ours(args):
     local_nnz = local_adj.nnz
     log("[rank %d] rows [%d,%d) nnz %d built in %.1fs" % (rank, lo, hi, local_nnz, time.time() - t0))
 
-    spmm = ShardedSpMM(local_adj, bounds, device=device)
-    sddmm = ShardedSDDMM(local_adj, bounds, device=device)
+    # C4 at N > 1: a shard of the R-MAT graph references a fraction of the feature rows, so only those are
+    # exchanged (all-to-all of the requested rows) where that pays; C2's rows reference nearly every column.
+    needed = None
+    if WORKLOAD == "C4" and world > 1 and not args.all_gather:
+        from featgraph_b200.sharded import NeededRows, needed_rows_pay
+        cand = NeededRows(local_adj, bounds, device=device)
+        log("[rank %d] needs %d of %d feature rows (%.2f)" % (rank, cand.n_compact, n, cand.fraction()))
+        if needed_rows_pay(cand):
+            needed = cand
+    spmm = ShardedSpMM(local_adj, bounds, device=device, needed_rows=needed)
+    sddmm = ShardedSDDMM(local_adj, bounds, device=device, needed_rows=needed)
+
+    def exchange_buffer(d):
+        if needed is not None:
+            from featgraph_b200.sharded import NeededFeatures
+            return NeededFeatures(needed, d, device=device)
+        return GatheredFeatures(bounds, d, device=device)
 
     # features: generated whole (seeded), each rank keeps its rows; pinned host copies for e2e
     feats = {}
@@ -363,12 +383,35 @@ def run_ours(args):
     # d and shared (GatheredFeatures); C4: X feeds SpMM, Y feeds SDDMM - two exchanges.
     shared = {d: GatheredFeatures(bounds, d, device=device) for d in dims} if WORKLOAD != "C4" else {}
     # C4 at N > 1: Y is not needed before the SDDMM, so its exchange runs beside the SpMM
-    c4_y = {d: GatheredFeatures(bounds, d, device=device) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
+    c4_y = {d: exchange_buffer(d) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
+    c4_x = {d: exchange_buffer(d) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
 
     prefetch = world > 1 and WORKLOAD != "C4" and not args.no_prefetch
     c4_overlap = bool(c4_y) and not args.no_prefetch
 
+    fused = None
+    if args.fused:
+        if WORKLOAD != "C4" or world != 1:
+            raise SystemExit("--fused is the one-GPU C4 step")
+        from featgraph import placeholder as _ph
+        from featgraph_b200.module import AggregateThenScore
+        fused = AggregateThenScore(local_adj, device=device)
+        fused.build([_ph((n, dims[0])), _ph((n, dims[0]))])
+
     def step(record=None):
+        if fused is not None:  # one call does both ops: its time is booked under "spmm", "sddmm" stays 0
+            for d in dims:
+                xd, yd = dev_feats[d]
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if record is not None else None
+                if ev:
+                    ev[0].record(stream)
+                    ev[1].record(stream)
+                fused.run([xd, yd])
+                if ev:
+                    for k in (2, 3, 4):
+                        ev[k].record(stream)
+                    record.append((d, ev))
+            return
         if prefetch:  # every feature matrix of the step is resident: exchange d[k+1] while d[k] computes
             shared[dims[0]].gather_async(dev_feats[dims[0]][0])
         for k, d in enumerate(dims):
@@ -378,26 +421,34 @@ def run_ours(args):
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if record is not None else None
             if ev:
                 ev[0].record(stream)
-            if WORKLOAD == "C4":
+            if WORKLOAD == "C4" and world > 1:
+                # X's exchange, then (beside the SpMM, unless --no-prefetch) Y's
+                c4_x[d].gather_async(xd)
+                if c4_overlap:
+                    c4_y[d].gather_async(yd)
+                gx = c4_x[d].wait()
+                if ev:
+                    ev[1].record(stream)
+                h = spmm.run(gx)
+                if ev:
+                    ev[2].record(stream)
+                if not c4_overlap:
+                    c4_y[d].gather_async(yd)
+                gy = c4_y[d].wait()
+                if ev:
+                    ev[3].record(stream)
+                sddmm.run(gy, h)  # column side Y (exchanged), row side H = A.X (local rows)
+            elif WORKLOAD == "C4":
                 spmm.gather(xd)
                 if ev:
                     ev[1].record(stream)
-                if c4_overlap:
-                    c4_y[d].gather_async(yd)
                 h = spmm.compute()
                 if ev:
                     ev[2].record(stream)
-                # column side Y (gathered), row side H = A.X (local rows)
-                if c4_overlap:
-                    gy = c4_y[d].wait()
-                else:
-                    sddmm.gather(yd)
+                sddmm.gather(yd)
                 if ev:
                     ev[3].record(stream)
-                if c4_overlap:
-                    sddmm.run(gy, h)
-                else:
-                    sddmm.compute(h)
+                sddmm.compute(h)
             else:
                 if prefetch:
                     if k + 1 < len(dims):
@@ -453,9 +504,23 @@ def run_ours(args):
     flops_per_step = sum(2 * 2.0 * nnz * d for d in dims)
     value = flops_per_step / (ms_per_step * 1e-3) / 1e9
 
+    # --- order-independent checksum of every output's bits, summed over ranks ---------------------
+    # (taken from the device-timed steps' outputs, before the end-to-end leg reuses the buffers)
+    # SpMM sums every element in storage order and SDDMM's tree is fixed per edge, so these values must
+    # be the same at every GPU count (the sharded outputs concatenate to the single-GPU output).
+    checksums = {}
+    for d in dims:
+        outs = (("spmm", fused.out), ("sddmm", fused.scores)) if fused is not None else \
+            (("spmm", spmm.out_cache[d][0]), ("sddmm", sddmm.out_cache[d][0]))
+        for op, t in outs:
+            c = t.contiguous().view(torch.int32).to(torch.int64).sum().reshape(1)
+            if world > 1:
+                dist.all_reduce(c, op=dist.ReduceOp.SUM)
+            checksums["%s_d%d" % (op, d)] = int(c.item())
+
     # --- end to end: host buffers in, host result out, every step -------------------------------
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and fused is None:
         from featgraph_b200 import sharded
         outs_host = {d: (torch.empty((hi - lo, d), dtype=torch.float32).pin_memory(),
                          torch.empty((local_nnz,), dtype=torch.float32).pin_memory()) for d in dims}
@@ -486,9 +551,16 @@ def run_ours(args):
             # issued first (they need only the copy-in stream), then the kernels, each followed by its
             # copy-out on the copy-out stream: a step costs about max(copies in, kernels, copies out).
             for d in dims:
-                e2e_x[d].gather_from_host_async(feats[d][0])
-                if WORKLOAD == "C4":
-                    e2e_y[d].gather_from_host_async(feats[d][1])
+                if WORKLOAD == "C4":  # copy this rank's rows in, then start both exchanges behind the copies
+                    s_in, _ = sharded.copy_streams(device)
+                    xs, ys = c4_stage[d]
+                    with torch.cuda.stream(s_in):
+                        xs.copy_(feats[d][0], non_blocking=True)
+                        ys.copy_(feats[d][1], non_blocking=True)
+                        e2e_x[d].gather_async(xs)
+                        e2e_y[d].gather_async(ys)
+                else:
+                    e2e_x[d].gather_from_host_async(feats[d][0])
             for d in dims:
                 spmm.build_cached(d, args.feat_tile)
                 sddmm.build_cached(d)
@@ -504,11 +576,13 @@ def run_ours(args):
                     sddmm.run_host(e2e_x[d], feats[d][1], outs_host[d][1])
             sharded.host_sync(device)
 
-        e2e_mod, e2e_x, e2e_y = {}, {}, {}
+        e2e_mod, e2e_x, e2e_y, c4_stage = {}, {}, {}, {}
         if world > 1:
-            e2e_x = {d: GatheredFeatures(bounds, d, device=device) for d in dims}
+            e2e_x = {d: exchange_buffer(d) for d in dims}
             if WORKLOAD == "C4":
-                e2e_y = {d: GatheredFeatures(bounds, d, device=device) for d in dims}
+                e2e_y = {d: exchange_buffer(d) for d in dims}
+                c4_stage = {d: (torch.empty((hi - lo, d), device=device), torch.empty((hi - lo, d), device=device))
+                            for d in dims}
         elif WORKLOAD != "C4":
             # deferred calls must not share staging buffers: one module per (op, d) for the e2e leg
             from featgraph import placeholder as _ph
@@ -543,17 +617,6 @@ def run_ours(args):
                           "through the sharded layer's host-buffer calls (gather_from_host_async / run_host: "
                           "copy-in and exchange of every feature matrix issued ahead of the kernels, results "
                           "leaving on a copy-out stream)")}
-
-    # --- order-independent checksum of every output's bits, summed over ranks ---------------------
-    # SpMM sums every element in storage order and SDDMM's tree is fixed per edge, so these values must
-    # be the same at every GPU count (the sharded outputs concatenate to the single-GPU output).
-    checksums = {}
-    for d in dims:
-        for op, t in (("spmm", spmm.out_cache[d][0]), ("sddmm", sddmm.out_cache[d][0])):
-            c = t.contiguous().view(torch.int32).to(torch.int64).sum().reshape(1)
-            if world > 1:
-                dist.all_reduce(c, op=dist.ReduceOp.SUM)
-            checksums["%s_d%d" % (op, d)] = int(c.item())
 
     # --- per-kernel table and roofline (per GPU: whole-graph bytes / N over the slowest rank's time) --
     peak, peak_kind = measured_peak_gbs()
@@ -608,11 +671,12 @@ def run_ours(args):
                    "dims": dims, "parallelism": "row-sharded x%d (nnz-balanced); each feature matrix all-gathered "
                    "once per step and d, inside the timed region%s" % (world, ", the exchange for the next d running beside "
                    "the current d's kernels" if prefetch else
-                                                  (", Y's exchange running beside the SpMM" if c4_overlap else ""))
+                                                  (", Y's exchange running beside the SpMM" if c4_overlap else "")) +
+                   ("; only the rows each shard references are exchanged (all-to-all)" if needed is not None else "")
                    if world > 1 else "single GPU",
                    "l2_policy": "inputs larger than L2 (CSR arrays %.0f MB per pass; 10 different kernels "
                                 "and feature matrices between repeats of any one)" % (8.0 * nnz / 1e6),
-                   "feat_tile": args.feat_tile or "auto",
+                   "feat_tile": args.feat_tile or "auto", "fused_call": bool(fused is not None),
                    "kernel_signature": _native.lib().fg_kernel_signature().decode()},
         "roofline": roofline, "kernels": kernels, "checksums": checksums, "e2e": e2e,
         "gpu_launches": launches, "clocks": clocks,

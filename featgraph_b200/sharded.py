@@ -328,17 +328,163 @@ class GatheredFeatures(_ShardedBase):
         return self
 
 
+# ---- exchanging only the rows a shard references ---------------------------------------------------------
+# An all-gather hands every rank every feature row.  A row shard's column ids reference only some of them:
+# nearly all on a graph whose rows each have hundreds of neighbours, a fraction on a skewed graph of millions
+# of vertices (R-MAT scale 22 on 8 ranks: about a third).  ``NeededRows`` works out, once per adjacency, which
+# rows each rank needs from each peer; per call every rank packs the rows its peers asked for (a small row-gather
+# kernel) and one all-to-all delivers them into a compact buffer.  The shard's column ids are remapped into that
+# buffer by an increasing map (position in the sorted list of needed ids), so every row's nonzeros keep their
+# order and every sum its bits.
+NEEDED_ROWS_MAX_FRACTION = 0.7  # the compact exchange is chosen while ranks need at most this share of the rows
+
+
+def _pack_rows(src, rows, out):
+    """out[i] = src[rows[i]] (rows: int64 tensor on src's device)."""
+    if rows.numel() == 0:
+        return out
+    if src.is_cuda:
+        import ctypes
+        from . import _native
+        with torch.cuda.device(src.device):
+            _native.check(_native.lib().fg_gather_rows_f32(
+                ctypes.c_void_p(src.data_ptr()), src.stride(0), ctypes.c_void_p(rows.data_ptr()), rows.numel(),
+                src.shape[1], ctypes.c_void_p(out.data_ptr()), out.stride(0),
+                ctypes.c_void_p(torch.cuda.current_stream(src.device).cuda_stream)))
+    else:  # CPU ranks (gloo): the host-side bookkeeping tests
+        torch.index_select(src, 0, rows, out=out)
+    return out
+
+
+class NeededRows(_ShardedBase):
+    """Which feature rows this rank's shard references, and which of its own rows each peer asked for.
+
+    ``adj``: the shard with column ids remapped into the compact buffer (``n_compact`` columns);
+    ``recv_counts[q]`` rows arrive from rank q, ``send_counts[p]`` rows go to rank p, ``send_rows`` lists the
+    local row ids to send, grouped by receiving rank."""
+
+    def __init__(self, local_adj, bounds, group=None, device=None):
+        super().__init__(bounds, group, device)
+        assert local_adj.shape[0] == self.row_hi - self.row_lo
+        needed = np.unique(local_adj.indices)
+        self.needed = needed
+        self.n_compact = int(needed.shape[0])
+        cut = np.searchsorted(needed, self.bounds)  # needed[cut[q]:cut[q+1]] live on rank q
+        self.recv_counts = np.diff(cut).astype(np.int64)
+        new_idx = np.searchsorted(needed, local_adj.indices).astype(local_adj.indices.dtype)
+        self.adj = scipy.sparse.csr_matrix((local_adj.data, new_idx, local_adj.indptr),
+                                           shape=(local_adj.shape[0], max(self.n_compact, 1)))
+        self.adj.has_sorted_indices = True
+        meta_dev = device if (device is not None and self.world > 1 and dist.get_backend(group) == "nccl") else None
+        if self.world == 1:
+            self.send_counts = self.recv_counts.copy()
+            self.send_rows = torch.from_numpy((needed - self.row_lo).astype(np.int64)).to(device)
+            return
+        # every rank learns how many rows each peer wants from it, then receives the lists themselves
+        mine = torch.from_numpy(self.recv_counts).to(meta_dev)
+        counts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(counts, mine, group=group)
+        table = torch.stack(counts).cpu().numpy()  # table[p][q]: rows rank p needs from rank q
+        self.send_counts = table[:, self.rank].astype(np.int64)
+        owner_start = np.repeat(self.bounds[:-1], self.recv_counts)
+        requests = torch.from_numpy((needed.astype(np.int64) - owner_start)).to(meta_dev)  # local ids at their owners
+        asked = torch.empty((int(self.send_counts.sum()),), dtype=torch.int64, device=meta_dev)
+        dist.all_to_all_single(asked, requests, output_split_sizes=[int(v) for v in self.send_counts],
+                               input_split_sizes=[int(v) for v in self.recv_counts], group=group)
+        self.send_rows = asked.to(device)
+
+    def fraction(self):
+        """Share of all feature rows this rank needs."""
+        return self.n_compact / float(max(int(self.bounds[-1]), 1))
+
+    def exchange(self, compact, x_local, send_buf=None, async_op=False):
+        """``compact[i] = features of needed[i]`` from whichever rank owns that row.  ``send_buf``: a reusable
+        [sum(send_counts), d] buffer.  Returns the work handle with ``async_op`` (NCCL), else ``compact``."""
+        d = x_local.shape[1]
+        if send_buf is None:
+            send_buf = torch.empty((int(self.send_counts.sum()), d), dtype=x_local.dtype, device=x_local.device)
+        _pack_rows(x_local, self.send_rows, send_buf)
+        if self.world == 1:
+            compact[:self.n_compact].copy_(send_buf)
+            return compact
+        try:
+            work = dist.all_to_all_single(compact[:self.n_compact], send_buf,
+                                          output_split_sizes=[int(v) for v in self.recv_counts],
+                                          input_split_sizes=[int(v) for v in self.send_counts], group=self.group,
+                                          async_op=async_op)
+        except Exception as exc:
+            raise ExchangeError("rank %d of %d: needed-rows exchange failed: %s" % (self.rank, self.world, exc)) from exc
+        return work if async_op else compact
+
+
+def needed_rows_pay(needed_rows, group=None):
+    """True if, averaged over the ranks, a shard references at most ``NEEDED_ROWS_MAX_FRACTION`` of the feature
+    rows (every rank gets the same answer: the choice of exchange must be collective)."""
+    frac = torch.tensor([needed_rows.fraction()], dtype=torch.float64)
+    if needed_rows.world > 1:
+        if dist.get_backend(group) == "nccl":
+            frac = frac.to(needed_rows.device)
+        dist.all_reduce(frac, group=group)
+        frac = frac / needed_rows.world
+    return float(frac.item()) <= NEEDED_ROWS_MAX_FRACTION
+
+
+class NeededFeatures:
+    """The compact counterpart of ``GatheredFeatures``: the feature rows this rank's shard references, fetched
+    by ``NeededRows.exchange``.  Same calls (``gather``, ``gather_async`` / ``wait``, ``.full``), so the sharded
+    ops built with ``needed_rows=`` take it in place of the local tensor."""
+
+    def __init__(self, needed_rows, feat_len, device=None):
+        self.rows = needed_rows
+        self.feat_len = int(feat_len)
+        self.device = device if device is not None else needed_rows.device
+        self.world, self.rank = needed_rows.world, needed_rows.rank
+        self.full = torch.zeros((max(needed_rows.n_compact, 1), self.feat_len), dtype=torch.float32, device=self.device)
+        self._send = torch.empty((int(needed_rows.send_counts.sum()), self.feat_len), dtype=torch.float32,
+                                 device=self.device)
+        self._work = None
+
+    def gather(self, x_local):
+        self.rows.exchange(self.full, x_local, self._send)
+        return self
+
+    def gather_async(self, x_local):
+        """Start the exchange behind the work already on the current stream; ``wait()`` before the first use."""
+        self._work = None
+        if self.world == 1 or dist.get_backend(self.rows.group) != "nccl":
+            return self.gather(x_local)
+        self._work = self.rows.exchange(self.full, x_local, self._send, async_op=True)
+        return self
+
+    def wait(self):
+        if self._work is not None:
+            try:
+                self._work.wait()
+            except Exception as exc:
+                raise ExchangeError("rank %d of %d: needed-rows exchange failed: %s" % (self.rank, self.world, exc)) from exc
+            self._work = None
+        return self
+
+
 class ShardedSpMM(_ShardedBase):
     """Row-sharded SpMM for a square adjacency.
 
     ``local_adj``: this rank's rows (``shard_csr_rows``), ``bounds``: the row ranges of all ranks
     (``nnz_balanced_row_ranges`` of the whole graph's indptr)."""
 
-    def __init__(self, local_adj, bounds, group=None, device=None):
+    def __init__(self, local_adj, bounds, group=None, device=None, needed_rows=None):
         from .module import VanillaSpMMcuda
         super().__init__(bounds, group, device)
         assert local_adj.shape[0] == self.row_hi - self.row_lo
         assert local_adj.shape[1] == int(self.bounds[-1]), "square adjacency expected (features are row-sharded)"
+        self.needed_rows = needed_rows
+        if needed_rows is not None:
+            # the kernel gathers from the compact buffer of needed rows (column ids remapped once)
+            self.n = max(needed_rows.n_compact, 1)
+            self.module = VanillaSpMMcuda(needed_rows.adj, device=device)
+            self.device = self.module.ctx
+            self.x_full = None
+            return
         # the kernel gathers from the all-gather buffer: in the padded layout the column ids are remapped once
         self.module = VanillaSpMMcuda(remap_columns(local_adj, self.bounds), device=device)
         self.device = self.module.ctx
@@ -351,6 +497,8 @@ class ShardedSpMM(_ShardedBase):
 
     def gather(self, x_local):
         """The exchange step alone: every rank's feature rows into this rank's ``x_full``."""
+        if self.needed_rows is not None:
+            return self.needed_rows.exchange(self.x_full, x_local)
         if self.world == 1:
             self.x_full = x_local
             return x_local
@@ -363,7 +511,7 @@ class ShardedSpMM(_ShardedBase):
     def run(self, x_local):
         """x_local: this rank's rows of the feature matrix, or a ``GatheredFeatures`` that already
         holds every rank's rows.  Returns this rank's rows of A.X."""
-        if isinstance(x_local, GatheredFeatures):
+        if isinstance(x_local, (GatheredFeatures, NeededFeatures)):
             return self.module.run([x_local.full])
         self.gather(x_local)
         return self.compute()
@@ -383,10 +531,17 @@ class ShardedSpMM(_ShardedBase):
 class ShardedSDDMM(_ShardedBase):
     """Edge-sharded SDDMM by the same row ranges (square adjacency)."""
 
-    def __init__(self, local_adj, bounds, group=None, device=None):
+    def __init__(self, local_adj, bounds, group=None, device=None, needed_rows=None):
         from .module import VanillaSDDMMcuda
         super().__init__(bounds, group, device)
         assert local_adj.shape[0] == self.row_hi - self.row_lo
+        self.needed_rows = needed_rows
+        if needed_rows is not None:
+            self.n = max(needed_rows.n_compact, 1)
+            self.module = VanillaSDDMMcuda(needed_rows.adj.tocoo(), device=device)
+            self.device = self.module.ctx
+            self.src_full = None
+            return
         self.module = VanillaSDDMMcuda(remap_columns(local_adj, self.bounds).tocoo(), device=device)
         self.device = self.module.ctx
         self.src_full = None
@@ -397,6 +552,8 @@ class ShardedSDDMM(_ShardedBase):
         self.src_full = torch.zeros((self.n, feat_len), dtype=torch.float32, device=self.device)
 
     def gather(self, src_local):
+        if self.needed_rows is not None:
+            return self.needed_rows.exchange(self.src_full, src_local)
         if self.world == 1:
             self.src_full = src_local
             return src_local
@@ -409,7 +566,7 @@ class ShardedSDDMM(_ShardedBase):
         """src_local: this rank's rows of the column-side matrix (gathered from all ranks), or a
         ``GatheredFeatures`` that already holds them; dst_local: this rank's rows of the row-side
         matrix.  Returns this rank's edges' dots."""
-        if isinstance(src_local, GatheredFeatures):
+        if isinstance(src_local, (GatheredFeatures, NeededFeatures)):
             return self.module.run([src_local.full, dst_local])
         self.gather(src_local)
         return self.compute(dst_local)

@@ -277,6 +277,15 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
 int fg_host_sync(void* stream);
 
 /* --------------------------------------------------------------------------------------
+ * Row gather: dst[i, :] = src[rows[i], :] for i < n_rows_out (int64 row ids on the device, trusted to be in
+ * range).  Plumbing of the multi-GPU layer, which has no counterpart in the reference (its modules are
+ * single-device, module/spmm.py:218): a rank packs the feature rows each peer's shard references into one
+ * send buffer for an all-to-all, instead of every rank receiving every row.  Strides in floats (0 = d).
+ * -------------------------------------------------------------------------------------- */
+int fg_gather_rows_f32(const float* d_src, int64_t ld_src, const int64_t* d_rows, int64_t n_rows_out, int32_t d,
+                       float* d_dst, int64_t ld_dst, void* stream);
+
+/* --------------------------------------------------------------------------------------
  * Index checks (the code generator of the reference emits shape asserts only; these add
  * the range checks that keep a bad adjacency from reading out of bounds).  Both
  * synchronise `stream` and return FG_ERR_BAD_INDEX with a message naming the first kind

@@ -90,6 +90,32 @@ def check_graph(graph, rank, world, device):
             np.testing.assert_array_equal(oh.numpy(), want)
             np.testing.assert_array_equal(eh.numpy(), e)
     assert spmm.padded == (graph == "power-law"), (graph, bounds)
+    if graph == "r-mat":
+        # the exchange of only the rows each shard references, over NCCL (all-to-all of the requested rows)
+        from featgraph_b200.sharded import NeededFeatures, NeededRows, needed_rows_pay
+        rows = NeededRows(local, bounds, device=device)
+        assert rows.n_compact < n and needed_rows_pay(rows) in (True, False)
+        spmm2 = ShardedSpMM(local, bounds, device=device, needed_rows=rows)
+        sddmm2 = ShardedSDDMM(local, bounds, device=device, needed_rows=rows)
+        d = 64
+        x = graphgen.uniform_features((n, d), seed=81)
+        y = graphgen.uniform_features((n, d), seed=82)
+        xl = torch.from_numpy(x[lo:hi].copy()).to(device)
+        yl = torch.from_numpy(y[lo:hi].copy()).to(device)
+        spmm2.build(d)
+        sddmm2.build(d)
+        gx, gy = NeededFeatures(rows, d, device=device), NeededFeatures(rows, d, device=device)
+        for _ in range(2):
+            gx.gather_async(xl)
+            gy.gather_async(yl)
+            h = spmm2.run(gx.wait())
+            e2 = sddmm2.run(gy.wait(), h)  # scores against the aggregate, as in the R-MAT step
+        want_h = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)
+        np.testing.assert_array_equal(h.cpu().numpy(), want_h[lo:hi])
+        want_e2 = oracle.sddmm(coo.row, coo.col, y, want_h)[adj.indptr[lo]:adj.indptr[hi]]
+        scale = max(float(np.abs(want_e2).max()), 1.0)
+        np.testing.assert_allclose(e2.cpu().numpy(), want_e2, rtol=1e-5, atol=1e-4 * scale)
+        np.testing.assert_array_equal(spmm2.run(xl).cpu().numpy(), want_h[lo:hi])  # the blocking form
 
 
 def check_full_size_shard(rank, world, device):

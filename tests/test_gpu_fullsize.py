@@ -200,3 +200,21 @@ def test_c4_rmat_aggregate_then_score(oracle):
     _, cols, _, idx = _sub_csr(adj, rows)
     row_of = np.repeat(rows, deg[rows]).astype(np.int32)
     np.testing.assert_array_equal(exact_e[idx], oracle.sddmm(row_of, cols, y, h))
+
+
+def test_c4_rmat_fused_aggregate_then_score(oracle):
+    """The same step through the fused call: H's sampled rows bit for bit, the sampled rows' scores within
+    the scaled tolerance (hub rows - the ring kernels plus the long-row scoring kernel - included)."""
+    from featgraph_b200 import graphgen
+    from featgraph_b200.module import AggregateThenScore
+    adj = graphgen.workload_graph("C4")
+    n = adj.shape[0]
+    rng = np.random.default_rng(5)
+    x = graphgen.workload_features("C4", n, 128, 0)
+    y = graphgen.workload_features("C4", n, 128, 1)
+    m = AggregateThenScore(adj)
+    m.build([placeholder((n, 128)), placeholder((n, 128))])
+    h_dev, s_dev = m.run([torch.from_numpy(x).to(m.ctx), torch.from_numpy(y).to(m.ctx)])
+    h, out_e = h_dev.cpu().numpy(), s_dev.cpu().numpy()
+    _check_spmm_sample(oracle, adj, x, h, rng, n_random=2000)
+    _check_sddmm_sample(oracle, adj, y, h, out_e, rng, n_random=2000, unit_scale=False)

@@ -175,3 +175,60 @@ def test_a_missing_peer_is_reported_not_waited_for_forever(tmp_path):
     assert os.path.exists(os.path.join(tmp_path, "left"))
     assert os.path.exists(os.path.join(tmp_path, "detected")), "rank 0 did not see an ExchangeError"
     assert float(open(os.path.join(tmp_path, "detected")).read()) < 60
+
+
+def _worker_needed_rows(rank, world, port, tmpdir):
+    """The needed-rows exchange on a skewed graph: every rank receives exactly the feature rows its shard's
+    column ids reference, the remapped shard indexes them, and the per-rank result equals the rows of the
+    whole product bit for bit (the remap is increasing, so every sum keeps its order)."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from featgraph_b200 import graphgen
+        from featgraph_b200.sharded import NeededFeatures, NeededRows, needed_rows_pay, shard_csr_rows
+        from featgraph_b200.util import nnz_balanced_row_ranges
+        adj = graphgen.rmat_graph(11, 4, seed=5)  # 2048 vertices, a few thousand edges: many untouched columns
+        n, d = adj.shape[0], 12
+        x = graphgen.uniform_features((n, d), seed=6)
+        y = graphgen.uniform_features((n, d), seed=7)
+        bounds = nnz_balanced_row_ranges(adj.indptr, world)
+        lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+        local = shard_csr_rows(adj, bounds, rank)
+        rows = NeededRows(local, bounds)
+        want_needed = np.unique(local.indices)
+        np.testing.assert_array_equal(rows.needed, want_needed)
+        assert rows.n_compact == len(want_needed) < n and rows.adj.shape == (hi - lo, len(want_needed))
+        assert int(rows.recv_counts.sum()) == len(want_needed)
+        assert needed_rows_pay(rows) in (True, False)
+        # what this rank sends: for each peer, that peer's needed ids inside [lo, hi), in ascending order
+        feats = NeededFeatures(rows, d)
+        for _ in range(2):  # twice: buffers are reused
+            feats.gather(torch.from_numpy(x[lo:hi].copy()))
+            np.testing.assert_array_equal(feats.full.numpy()[:rows.n_compact], x[want_needed])
+        np.testing.assert_array_equal(feats.full.numpy()[rows.adj.indices], x[local.indices])
+        whole = oracle.spmm_csr(adj.indptr, adj.indices, adj.data, x)
+        mine = oracle.spmm_csr(rows.adj.indptr, rows.adj.indices, rows.adj.data, feats.full.numpy())
+        np.testing.assert_array_equal(mine, whole[lo:hi])
+        coo = adj.tocoo()
+        whole_e = oracle.sddmm(coo.row, coo.col, x, y)
+        lc = rows.adj.tocoo()
+        mine_e = oracle.sddmm(lc.row, lc.col, feats.full.numpy(), y[lo:hi])
+        np.testing.assert_array_equal(mine_e, whole_e[adj.indptr[lo]:adj.indptr[hi]])
+        feats.gather_async(torch.from_numpy(y[lo:hi].copy())).wait()  # gloo: the blocking path
+        np.testing.assert_array_equal(feats.full.numpy()[:rows.n_compact], y[want_needed])
+        open(os.path.join(tmpdir, "ok%d" % rank), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_needed_rows_exchange_on_cpu_ranks(tmp_path, world):
+    import oracle
+    oracle.build()
+    from featgraph_b200 import build
+    build.build_graphgen()
+    mp.spawn(_worker_needed_rows, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == ["ok%d" % r for r in range(world)]
