@@ -6,8 +6,8 @@ package (0.23.dev0) can lower that compute definition with te.create_prim_func a
 C backend (default loop nest: edge outer, k ascending inner - the order of the reference's x86
 schedule, which for num_feat_partitions > 1 only hoists the outer part of k, op/vanilla_sddmm.py:66-74).
 This script loads the reference file by path, runs it on seeded inputs and stores inputs' seeds and
-outputs.  The reference's SpMM definitions do not lower in that fork (data-dependent reduce extent),
-so SpMM has no such fixture.
+outputs.  (The SpMM definitions need one repair before that fork compiles them; their fixture is made by
+make_spmm_reference_golden.py beside this file.)
 
     python tests/golden/make_sddmm_reference_golden.py [path-to-reference-checkout]
 """
