@@ -277,6 +277,32 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
 int fg_host_sync(void* stream);
 
 /* --------------------------------------------------------------------------------------
+ * Generalized forms (off the benchmarked path).  The reference checkout has none: its README (lines 9-11)
+ * only points to a branch with "generalized SpMM and generalized SDDMM w/ broadcasting", so the semantics are
+ * stated here rather than matched:
+ *   fg_spmm_csr_reduce_f32   out[r, f] = reduce over the row's nonzeros of vals[e] * x[indices[e], f], with
+ *                            reduce = FG_REDUCE_MAX, FG_REDUCE_MIN or FG_REDUCE_MEAN (the sum in storage order,
+ *                            divided by the row's nonzero count).  A row without nonzeros gives 0.  d_vals may
+ *                            be NULL (all ones).  The sum itself is fg_spmm_csr_f32.
+ *   fg_edge_binary_f32       out[e, f] = src[col[e], f] (op) dst[row[e], f] with op = FG_EDGE_ADD, FG_EDGE_SUB or
+ *                            FG_EDGE_MUL: a vector per edge, [nnz, d] (the dot product of FG_EDGE_MUL's rows is
+ *                            fg_sddmm_coo_f32).  Edges in any order.
+ * Strides in floats (0 = d); any d; 128-bit accesses where d, the strides and the bases allow.
+ * -------------------------------------------------------------------------------------- */
+#define FG_REDUCE_MAX 1
+#define FG_REDUCE_MIN 2
+#define FG_REDUCE_MEAN 3
+#define FG_EDGE_ADD 0
+#define FG_EDGE_SUB 1
+#define FG_EDGE_MUL 2
+int fg_spmm_csr_reduce_f32(const int32_t* d_indptr, const int32_t* d_indices, const float* d_vals, const float* d_x,
+                           int64_t ldx, float* d_out, int64_t ldo, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                           int32_t reduce, void* stream);
+int fg_edge_binary_f32(const int32_t* d_row, const int32_t* d_col, const float* d_src, int64_t ld_src, const float* d_dst,
+                       int64_t ld_dst, float* d_out, int64_t ldo, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
+                       int32_t op, void* stream);
+
+/* --------------------------------------------------------------------------------------
  * Row gather: dst[i, :] = src[rows[i], :] for i < n_rows_out (int64 row ids on the device, trusted to be in
  * range).  Plumbing of the multi-GPU layer, which has no counterpart in the reference (its modules are
  * single-device, module/spmm.py:218): a rank packs the feature rows each peer's shard references into one
