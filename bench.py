@@ -158,16 +158,17 @@ class ClockSampler:
 # CPU leg: the oracle (a restatement of the reference's x86 loop nests) timed on host cores.
 # ----------------------------------------------------------------------------------------------
 SDDMM_SAMPLE_DIV = 64  # the single-threaded SDDMM is timed on the first nnz / 64 edges
+SPMM_SAMPLE_DIV = 4    # the all-threads SpMM on the first n / 4 rows (rows are independent, degrees i.i.d.)
 
 
 class CpuStep:
     """One bounded sample of the step on the host cores, as the reference's x86 path would run it: at
-    EVERY feature length of the step, SpMM on the whole graph with every host thread (row-parallel, with
-    the layout copies the reference's timed function contains, python/featgraph/op/vanilla_spmm.py:41-62)
-    and SDDMM on ONE thread (the reference's x86 SDDMM schedule has no parallel loop,
-    python/featgraph/op/vanilla_sddmm.py:66-74) on the first nnz / 64 edges.  The step rate is formed
-    from all feature lengths: FLOPs of a full step / (sum of SpMM times + sum of SDDMM sample times scaled
-    to all edges)."""
+    EVERY feature length of the step, SpMM on the first quarter of the rows with every host thread
+    (row-parallel, with the layout copies the reference's timed function contains,
+    python/featgraph/op/vanilla_spmm.py:41-62) and SDDMM on ONE thread (the reference's x86 SDDMM schedule
+    has no parallel loop, python/featgraph/op/vanilla_sddmm.py:66-74) on the first nnz / 64 edges.  The
+    step rate is formed from all feature lengths: FLOPs of a full step / (sum of the SpMM and SDDMM sample
+    times, each scaled to the whole graph)."""
 
     def __init__(self, adj, dims):
         import oracle
@@ -179,7 +180,10 @@ class CpuStep:
         self.col = adj.indices[:self.ne]
         self.x = {d: graphgen.workload_features(WORKLOAD, n, d, 0) for d in dims}
         self.y = {d: graphgen.workload_features(WORKLOAD, n, d, 1) for d in dims}
-        self.out = {d: np.empty((n, d), dtype=np.float32) for d in dims}
+        self.rows = max(1, n // SPMM_SAMPLE_DIV)
+        self.sub_ptr = np.ascontiguousarray(adj.indptr[:self.rows + 1])
+        self.sub_nnz = int(self.sub_ptr[-1])
+        self.out = {d: np.empty((self.rows, d), dtype=np.float32) for d in dims}
         self.oe = np.empty(self.ne, dtype=np.float32)
         self.threads = oracle.num_threads()
 
@@ -188,7 +192,8 @@ class CpuStep:
         o, adj, t = self.oracle, self.adj, {}
         for d in self.dims:
             t0 = time.perf_counter()
-            o.spmm_csr(adj.indptr, adj.indices, adj.data, self.x[d], with_copies=True, out=self.out[d])
+            o.spmm_csr(self.sub_ptr, adj.indices[:self.sub_nnz], adj.data[:self.sub_nnz], self.x[d], with_copies=True,
+                       out=self.out[d])
             t1 = time.perf_counter()
             o.sddmm(self.row, self.col, self.x[d], self.y[d], threads=1, out=self.oe)
             t[d] = (t1 - t0, time.perf_counter() - t1)
@@ -197,17 +202,19 @@ class CpuStep:
     def summarise(self, runs):
         """Mean times over ``runs`` (a list of run() results) -> rates."""
         nnz, scale = self.adj.nnz, self.adj.nnz / float(self.ne)
+        scale_spmm = nnz / float(max(self.sub_nnz, 1))
         per_d, est_step, sample = {}, 0.0, 0.0
         for d in self.dims:
             ts = float(np.mean([r[d][0] for r in runs]))
             te = float(np.mean([r[d][1] for r in runs]))
-            per_d[d] = {"spmm_s": ts, "spmm_gflops": 2.0 * nnz * d / ts / 1e9,
+            per_d[d] = {"spmm_sample_s": ts, "spmm_gflops": 2.0 * self.sub_nnz * d / ts / 1e9,
                         "sddmm_sample_s": te, "sddmm_gflops": 2.0 * self.ne * d / te / 1e9}
-            est_step += ts + te * scale
+            est_step += ts * scale_spmm + te * scale
             sample += ts + te
         flops = sum(2 * 2.0 * nnz * d for d in self.dims)
         return {"step_gflops": flops / est_step / 1e9, "estimated_full_step_s": est_step, "sample_s": sample,
-                "per_d": per_d, "threads": self.threads, "sddmm_edges": self.ne}
+                "per_d": per_d, "threads": self.threads, "sddmm_edges": self.ne, "spmm_rows": self.rows,
+                "spmm_nnz": self.sub_nnz}
 
     def extras(self, d=64):
         """Variants that are not the reference's schedule, once each at one feature length: SpMM with
@@ -221,20 +228,21 @@ class CpuStep:
             fn()
             return time.perf_counter() - t0
 
-        t_dyn = timed(lambda: o.spmm_csr(adj.indptr, adj.indices, adj.data, self.x[d], dynamic=True, out=self.out[d]))
+        t_dyn = timed(lambda: o.spmm_csr(self.sub_ptr, adj.indices[:self.sub_nnz], adj.data[:self.sub_nnz], self.x[d],
+                                         dynamic=True, out=self.out[d]))
         t_mt = timed(lambda: o.sddmm(self.row, self.col, self.x[d], self.y[d], threads=self.threads, out=self.oe))
         rows = max(1, adj.shape[0] // 8)  # scipy is single-threaded: an eighth of the rows bounds its time
         sub = adj[:rows]
         t_sp = timed(lambda: sub.dot(self.x[d]))
-        return {"d": d, "spmm_dynamic_nocopy_gflops": 2.0 * adj.nnz * d / t_dyn / 1e9,
+        return {"d": d, "spmm_dynamic_nocopy_gflops": 2.0 * self.sub_nnz * d / t_dyn / 1e9,
                 "sddmm_openmp_gflops": 2.0 * self.ne * d / t_mt / 1e9,
                 "scipy_csr_dot_1thread_gflops": 2.0 * sub.nnz * d / t_sp / 1e9, "scipy_rows": rows}
 
     def sample_text(self):
-        return ("at each d in %s: SpMM on the whole graph (all %d threads, with the reference's layout copies); "
-                "SDDMM on one thread (the reference's x86 SDDMM has no parallel loop) on the first %d edges, scaled "
-                "to all edges; rate = FLOPs of a full step / estimated full-step time"
-                % (self.dims, self.threads, self.ne))
+        return ("at each d in %s: SpMM on the first %d rows (%d nonzeros; all %d threads, with the reference's layout "
+                "copies); SDDMM on one thread (the reference's x86 SDDMM has no parallel loop) on the first %d edges; "
+                "both scaled to the whole graph; rate = FLOPs of a full step / estimated full-step time"
+                % (self.dims, self.rows, self.sub_nnz, self.threads, self.ne))
 
 
 def workload_text(n, nnz):
