@@ -146,3 +146,24 @@ def test_loading_the_library_rebuilds_it_when_a_source_is_newer(monkeypatch):
     monkeypatch.setattr(_native, "_lib", None)
     _native.lib()
     assert asked == []
+
+
+def test_ncu_traffic_table_is_tied_to_the_kernel_signature():
+    """bench.py trusts profiles/ncu_traffic.json only while the loaded library reports the kernel shapes the
+    table was captured from; any other signature makes the table 'stale' instead of silently wrong."""
+    import importlib.util
+    import json
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    rec = json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json")))
+    assert sorted((c["op"], c["d"]) for c in rec["calls"]) == sorted(
+        (op, d) for op in ("spmm", "sddmm") for d in (32, 64, 128, 256, 512))
+    table, note = bench.load_ncu_traffic(rec["kernel_signature"])
+    assert len(table) == 10 and all(v > 0 for v in table.values()) and "stale" not in note
+    table, note = bench.load_ncu_traffic(rec["kernel_signature"] + "+changed")
+    assert table == {} and "stale" in note
+    from featgraph_b200 import _native
+    assert _native.lib().fg_kernel_signature().decode() == rec["kernel_signature"], \
+        "kernel shapes changed since profiles/ncu_traffic.json was captured: re-capture it " \
+        "(python -m featgraph_b200.benchmark.ncu_traffic)"
