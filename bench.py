@@ -77,7 +77,10 @@ def parse_args():
                         "each shard references would be chosen")
     p.add_argument("--fused", action="store_true",
                    help="C4 on one GPU: the fused aggregate-then-score call instead of SpMM followed by SDDMM")
-    p.add_argument("--e2e-steps", type=int, default=2)
+    p.add_argument("--e2e-steps", type=int, default=4)
+    p.add_argument("--e2e-tiled-sddmm", action="store_true",
+                   help="end-to-end leg on one GPU: SDDMM through column windows of feature tiles even where the "
+                        "one-pass kernel over column blocks would be used")
     return p.parse_args()
 
 
@@ -536,7 +539,7 @@ def run_ours(args):
         if WORKLOAD == "C4":
             h2d = sum(2 * (hi - lo) * d * 4 for d in dims) + (sum((hi - lo) * d * 4 for d in dims) if world == 1 else 0)
         else:
-            h2d = sum((3 if world == 1 else 2) * (hi - lo) * d * 4 for d in dims)
+            h2d = sum(2 * (hi - lo) * d * 4 for d in dims)  # X_d once (shared by both ops) and Y_d
         d2h = sum((hi - lo) * d * 4 + local_nnz * 4 for d in dims)
 
         def e2e_step():
@@ -550,8 +553,10 @@ def run_ours(args):
                         hh = spmm.module.run_host([xh], out=outs_host[d][0])
                         sddmm.module.run_host([yh, hh], out=outs_host[d][1])
                     else:  # deferred completion: one call's copy-out overlaps the next call
+                        # (the SDDMM scores the features the SpMM call has just uploaded: X goes over PCIe once)
                         e2e_mod[("spmm", d)].run_host([xh], out=outs_host[d][0], wait=False)
-                        e2e_mod[("sddmm", d)].run_host([xh, yh], out=outs_host[d][1], wait=False)
+                        e2e_mod[("sddmm", d)].run_host([e2e_mod[("spmm", d)].device_input, yh], out=outs_host[d][1],
+                                                       wait=False)
                 featgraph_b200.host_sync(device)
                 stream.synchronize()
                 return
@@ -600,7 +605,7 @@ def run_ours(args):
                 m1 = _SP(local_adj, device=device)
                 m1.build([_ph((n, d))], {}, {})
                 m2 = _SD(coo_local, device=device)
-                m2.build([_ph((n, d)), _ph((n, d))], {}, {})
+                m2.build([_ph((n, d)), _ph((n, d))], {}, {"col_blocks": 1} if args.e2e_tiled_sddmm else {})
                 e2e_mod[("spmm", d)], e2e_mod[("sddmm", d)] = m1, m2
 
         e2e_step()

@@ -40,6 +40,7 @@ SIGNATURES = {
     "fg_sddmm_coo_f32_exact": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fg_spmm_csr_f32_host": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "fg_sddmm_coo_f32_host": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "fg_sddmm_coo_f32_planned_host": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fg_host_sync": (ctypes.c_int, [_vp]),
     "fg_spmm_csr_reduce_f32": (ctypes.c_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "fg_edge_binary_f32": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),

@@ -132,7 +132,9 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
                         (long long)n_rows, (long long)n_cols, (long long)nnz, d);
     if (chunk < 0 || (chunk % 4 != 0)) return fg::fail(FG_ERR_INVALID_ARGUMENT, "chunk must be 0 or a multiple of 4");
     if (nnz == 0) return FG_OK;
-    if (!h_src || !h_dst || !h_out || !d_src_staging || !d_dst_staging || !d_out_staging)
+    // h_src == NULL: the column-side matrix is already on the device, in d_src_staging (e.g. uploaded by an SpMM
+    // host call on the same features just before: a layer that runs both ops uploads them once)
+    if (!h_dst || !h_out || !d_src_staging || !d_dst_staging || !d_out_staging)
         return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL host or staging buffer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     Pipeline* pp = pipeline();
@@ -151,7 +153,7 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
         const int wc = d - c0 < w ? d - c0 : w;
         cudaEvent_t in_done;
         FG_TRY_RC(p.event(&in_done));
-        FG_CUDA_TRY(copy_window(d_src_staging, h_src, n_cols, d, c0, wc, cudaMemcpyHostToDevice, p.in));
+        if (h_src) FG_CUDA_TRY(copy_window(d_src_staging, h_src, n_cols, d, c0, wc, cudaMemcpyHostToDevice, p.in));
         FG_CUDA_TRY(copy_window(d_dst_staging, h_dst, n_rows, d, c0, wc, cudaMemcpyHostToDevice, p.in));
         FG_CUDA_TRY(cudaEventRecord(in_done, p.in));
         FG_CUDA_TRY(cudaStreamWaitEvent(s, in_done, 0));
@@ -161,6 +163,46 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
     // the result leaves on the copy-out stream, so that a following call's kernels need not wait for it
     cudaEvent_t k_done;
     FG_TRY_RC(p.event(&k_done));
+    FG_CUDA_TRY(cudaEventRecord(k_done, s));
+    FG_CUDA_TRY(cudaStreamWaitEvent(p.out, k_done, 0));
+    FG_CUDA_TRY(cudaMemcpyAsync(h_out, d_out_staging, sizeof(float) * nnz, cudaMemcpyDeviceToHost, p.out));
+    if (deferred) return FG_OK;
+    FG_CUDA_TRY(cudaStreamSynchronize(p.out));
+    FG_CUDA_TRY(cudaStreamSynchronize(s));
+    return FG_OK;
+}
+
+int fg_sddmm_coo_f32_planned_host(const fg_sddmm_plan* plan, const int32_t* d_col, const float* d_src, const float* h_dst,
+                                  float* h_out, float* d_dst_staging, float* d_out_staging, int64_t n_rows, int64_t n_cols,
+                                  int64_t nnz, int32_t d, int32_t flags, void* stream) {
+    if (d < 1 || n_rows < 0 || n_cols < 0 || nnz < 0)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "bad sizes n_rows=%lld n_cols=%lld nnz=%lld d=%d",
+                        (long long)n_rows, (long long)n_cols, (long long)nnz, d);
+    if (nnz == 0) return FG_OK;
+    if (!plan || !d_src || !h_dst || !h_out || !d_dst_staging || !d_out_staging)
+        return fg::fail(FG_ERR_INVALID_ARGUMENT, "NULL plan, host or staging buffer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    Pipeline* pp = pipeline();
+    if (!pp) return fg::fail(FG_ERR_CUDA, "no current CUDA device (or its ordinal is beyond %d)", fg::kMaxDevices);
+    Pipeline& p = *pp;
+    FG_TRY_RC(p.prepare());
+    const bool deferred = (flags & FG_HOST_DEFERRED) != 0;
+    if (!deferred) {  // the staging buffers may still be in use by earlier work on the caller's stream
+        cudaEvent_t start;
+        FG_TRY_RC(p.event(&start));
+        FG_CUDA_TRY(cudaEventRecord(start, s));
+        FG_CUDA_TRY(cudaStreamWaitEvent(p.in, start, 0));
+    }
+    // the one-pass kernel needs whole rows: the row-side matrix goes in as one copy, beside whatever the
+    // caller's stream is still computing; the column side is on the device already
+    cudaEvent_t in_done, k_done;
+    FG_TRY_RC(p.event(&in_done));
+    FG_TRY_RC(p.event(&k_done));
+    FG_CUDA_TRY(copy_window(d_dst_staging, h_dst, n_rows, d, 0, d, cudaMemcpyHostToDevice, p.in));
+    FG_CUDA_TRY(cudaEventRecord(in_done, p.in));
+    FG_CUDA_TRY(cudaStreamWaitEvent(s, in_done, 0));
+    FG_TRY_RC(fg_sddmm_coo_f32_planned(plan, d_col, d_src, d, d_dst_staging, d, d_out_staging, n_rows, n_cols, nnz, d, 0,
+                                       stream));
     FG_CUDA_TRY(cudaEventRecord(k_done, s));
     FG_CUDA_TRY(cudaStreamWaitEvent(p.out, k_done, 0));
     FG_CUDA_TRY(cudaMemcpyAsync(h_out, d_out_staging, sizeof(float) * nnz, cudaMemcpyDeviceToHost, p.out));

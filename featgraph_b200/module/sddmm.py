@@ -209,10 +209,16 @@ class SDDMMbase:
             raise RuntimeError("call build() before run_host()")
         dev.refuse_if_deferred_pending(self)
         ts = [torch.from_numpy(x) if isinstance(x, np.ndarray) else x for x in inputs]
-        for t, shape in zip(ts, self._shapes):
-            if t.device.type != "cpu" or t.dtype != torch.float32 or not t.is_contiguous() \
+        # The column-side matrix may already be on the device (a CUDA tensor of the right shape, e.g.
+        # ``VanillaSpMM*.device_input`` after that module's run_host on the same features): it is then used where it
+        # is, not copied - a layer that runs both ops uploads its features once.
+        src_resident = ts[0].device == self._device
+        for k, (t, shape) in enumerate(zip(ts, self._shapes)):
+            on_host = t.device.type == "cpu"
+            if not (on_host or (k == 0 and src_resident)) or t.dtype != torch.float32 or not t.is_contiguous() \
                     or tuple(t.shape) != tuple(shape):
-                raise ValueError("run_host wants contiguous float32 host arrays of shapes %s" % (self._shapes,))
+                raise ValueError("run_host wants contiguous float32 host arrays of shapes %s (the first may be a "
+                                 "tensor on the module's device)" % (self._shapes,))
         if out is None:
             out = torch.empty((self._nnz,), dtype=torch.float32).pin_memory()
         if out.device.type != "cpu" or out.dtype != torch.float32 or tuple(out.shape) != (self._nnz,):
@@ -220,12 +226,25 @@ class SDDMMbase:
         import ctypes
         d = self._shapes[0][1]
         with torch.cuda.device(self._device):
-            if self._staging is None or tuple(self._staging[0].shape) != tuple(self._shapes[0]):
-                self._staging = (torch.empty(self._shapes[0], dtype=torch.float32, device=self._device),
+            if self._staging is None or tuple(self._staging[1].shape) != tuple(self._shapes[1]) \
+                    or (not src_resident and tuple(self._staging[0].shape) != tuple(self._shapes[0])):
+                self._staging = (torch.empty(self._shapes[0] if not src_resident else (0, d), dtype=torch.float32,
+                                             device=self._device),
                                  torch.empty(self._shapes[1], dtype=torch.float32, device=self._device))
+            src_dev = ts[0] if src_resident else self._staging[0]
+            if src_resident and self._plan is not None and chunk == 0:
+                # column side on the device, matrix larger than L2: the one-pass kernel over column blocks
+                dev.check(dev.lib().fg_sddmm_coo_f32_planned_host(
+                    self._plan, dev.ptr(self._adj_col), dev.ptr(src_dev), ctypes.c_void_p(ts[1].data_ptr()),
+                    ctypes.c_void_p(out.data_ptr()), dev.ptr(self._staging[1]), dev.ptr(self.out), self._num_rows,
+                    self._num_cols, self._nnz, d, 0 if wait else 1, dev.stream_ptr(self._device)))
+                if not wait:
+                    self._deferred_epoch = dev.sync_epoch(self._device)
+                return out
             dev.check(dev.lib().fg_sddmm_coo_f32_host(
-                dev.ptr(self._adj_row), dev.ptr(self._adj_col), ctypes.c_void_p(ts[0].data_ptr()),
-                ctypes.c_void_p(ts[1].data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(self._staging[0]),
+                dev.ptr(self._adj_row), dev.ptr(self._adj_col),
+                ctypes.c_void_p(0) if src_resident else ctypes.c_void_p(ts[0].data_ptr()),
+                ctypes.c_void_p(ts[1].data_ptr()), ctypes.c_void_p(out.data_ptr()), dev.ptr(src_dev),
                 dev.ptr(self._staging[1]), dev.ptr(self.out), self._num_rows, self._num_cols, self._nnz, d,
                 self._rows_sorted, int(chunk), 0 if wait else 1, dev.stream_ptr(self._device)))
             if not wait:

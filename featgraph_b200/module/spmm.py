@@ -203,6 +203,13 @@ class SpMMbase:
         return dev.time_calls(lambda: self._launch(inputs[0], self.out), self._device, num_runs)
 
     @property
+    def device_input(self):
+        """The device copy of the features of the last ``run_host`` call (complete once the work enqueued by that
+        call has run on the current stream): hand it to ``VanillaSDDMM*.run_host`` as the column-side matrix to
+        score the same features without uploading them again."""
+        return self._x_staging
+
+    @property
     def ctx(self):
         """The device the module runs on (a ``torch.device``)."""
         return self._device

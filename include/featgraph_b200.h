@@ -262,6 +262,9 @@ int fg_sddmm_coo_f32_exact(const int32_t* d_row, const int32_t* d_col, const flo
  *          copy-out of one call overlap the copy-in and kernels of the next.  The caller promises
  *          that the staging buffers of a deferred call are not touched by anything else (another
  *          call with the same buffers included) until that fg_host_sync.
+ *   h_src  of the SDDMM call may be NULL: the column-side matrix is then taken as already present in
+ *          d_src_staging, complete by the time `stream` reaches this call - e.g. the d_x_staging of an SpMM host
+ *          call on the same features enqueued just before, so that a layer running both ops uploads them once.
  * -------------------------------------------------------------------------------------- */
 #define FG_HOST_DEFERRED 1
 int fg_spmm_csr_f32_host(const fg_row_schedule* schedule, const int32_t* d_indptr,
@@ -272,6 +275,12 @@ int fg_sddmm_coo_f32_host(const int32_t* d_row, const int32_t* d_col, const floa
                           const float* h_dst, float* h_out, float* d_src_staging, float* d_dst_staging,
                           float* d_out_staging, int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t d,
                           int32_t rows_sorted, int32_t chunk, int32_t flags, void* stream);
+/* The host-buffer form of fg_sddmm_coo_f32_planned for a column-side matrix that is already on the device
+ * (d_src, dense rows of d floats): the row-side matrix is copied in whole beside the caller's earlier work, the
+ * one-pass kernel runs, the result leaves on the copy-out stream.  flags as above. */
+int fg_sddmm_coo_f32_planned_host(const fg_sddmm_plan* plan, const int32_t* d_col, const float* d_src, const float* h_dst,
+                                  float* h_out, float* d_dst_staging, float* d_out_staging, int64_t n_rows, int64_t n_cols,
+                                  int64_t nnz, int32_t d, int32_t flags, void* stream);
 /* Wait until every host-buffer call issued by this host thread (on `stream` and on the library's
  * copy streams) has finished. */
 int fg_host_sync(void* stream);

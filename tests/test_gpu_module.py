@@ -109,6 +109,20 @@ def test_host_buffer_calls_pipeline_windows_and_match_device_calls(oracle, d, ch
     featgraph_b200.host_sync()
     np.testing.assert_array_equal(o1.numpy(), want)
     np.testing.assert_allclose(o2.numpy(), oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)
+    # the SDDMM host call takes the features the SpMM host call has just uploaded, without copying them again
+    sp_.run_host([xp], out=o1, chunk=chunk, wait=False)
+    o3 = torch.zeros((coo.nnz,)).pin_memory()
+    sd.run_host([sp_.device_input, yp], out=o3, chunk=chunk, wait=False)
+    featgraph_b200.host_sync()
+    np.testing.assert_array_equal(o3.numpy(), o2.numpy())
+    # with column blocks planned, the resident form runs the one-pass kernel (same dot products to rounding)
+    sd.build([placeholder((n, d)), placeholder((n, d))], {}, {"col_blocks": 3})
+    if sd._plan is not None:
+        sp_.run_host([xp], out=o1, chunk=chunk, wait=False)
+        sd.run_host([sp_.device_input, yp], out=o3, wait=False)
+        featgraph_b200.host_sync()
+        np.testing.assert_allclose(o3.numpy(), oracle.sddmm(coo.row, coo.col, x, y), rtol=RTOL, atol=ATOL)
+    sd.build([placeholder((n, d)), placeholder((n, d))], {}, {})
     # ... and is usable again after host_sync()
     np.testing.assert_array_equal(sp_.run_host([xp], out=o1, chunk=chunk).numpy(), want)
 
