@@ -167,3 +167,19 @@ def test_ncu_traffic_table_is_tied_to_the_kernel_signature():
     assert _native.lib().fg_kernel_signature().decode() == rec["kernel_signature"], \
         "kernel shapes changed since profiles/ncu_traffic.json was captured: re-capture it " \
         "(python -m featgraph_b200.benchmark.ncu_traffic)"
+
+
+def test_header_is_plain_c():
+    """The boundary is a C ABI: include/featgraph_b200.h must compile as C99 on its own."""
+    import shutil
+    import subprocess
+    import tempfile
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if not cc:
+        pytest.skip("no C compiler")
+    with tempfile.TemporaryDirectory() as tmp:
+        src = os.path.join(tmp, "use_header.c")
+        open(src, "w").write('#include "featgraph_b200.h"\nint main(void) { return FG_OK; }\n')
+        r = subprocess.run([cc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"),
+                            "-fsyntax-only", src], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
