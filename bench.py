@@ -72,6 +72,9 @@ def parse_args():
     p.add_argument("--no-prefetch", action="store_true",
                    help="N > 1: exchange each feature matrix right before its ops instead of during the previous ones")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--exchange", choices=("all-gather", "peer-copy"), default="all-gather",
+                   help="N > 1, device-timed steps: how the feature rows are exchanged - the backend's all-gather, or one "
+                        "device-to-device copy per peer into symmetric memory (copy engines, no SMs)")
     p.add_argument("--all-gather", action="store_true",
                    help="C4 at N > 1: exchange whole feature matrices (all-gather) even where exchanging only the rows "
                         "each shard references would be chosen")
@@ -392,7 +395,9 @@ def run_ours(args):
 
     # C2/C3: both ops of a step gather from the same feature matrix X_d, so it is exchanged once per
     # d and shared (GatheredFeatures); C4: X feeds SpMM, Y feeds SDDMM - two exchanges.
-    shared = {d: GatheredFeatures(bounds, d, device=device) for d in dims} if WORKLOAD != "C4" else {}
+    shared = {d: GatheredFeatures(bounds, d, device=device, peer_copy=args.exchange == "peer-copy") for d in dims} \
+        if WORKLOAD != "C4" else {}
+    exchange_kind = shared[dims[0]].exchange if shared else ("needed-rows" if needed is not None else "all-gather")
     # C4 at N > 1: Y is not needed before the SDDMM, so its exchange runs beside the SpMM
     c4_y = {d: exchange_buffer(d) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
     c4_x = {d: exchange_buffer(d) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
@@ -689,6 +694,7 @@ def run_ours(args):
                    if world > 1 else "single GPU",
                    "l2_policy": "inputs larger than L2 (CSR arrays %.0f MB per pass; 10 different kernels "
                                 "and feature matrices between repeats of any one)" % (8.0 * nnz / 1e6),
+                   "exchange": exchange_kind if world > 1 else None,
                    "feat_tile": args.feat_tile or "auto", "fused_call": bool(fused is not None),
                    "kernel_signature": _native.lib().fg_kernel_signature().decode()},
         "roofline": roofline, "kernels": kernels, "checksums": checksums, "e2e": e2e,

@@ -226,16 +226,35 @@ class GatheredFeatures(_ShardedBase):
     would double the NVLink traffic.  ``gather(x_local)`` returns ``self``; pass it to
     ``ShardedSpMM.run`` / ``ShardedSDDMM.run`` in place of the local tensor."""
 
-    def __init__(self, bounds, feat_len, group=None, device=None):
+    def __init__(self, bounds, feat_len, group=None, device=None, peer_copy=False):
         super().__init__(bounds, group, device)
         self.feat_len = int(feat_len)
-        self.full = torch.zeros((self.n, self.feat_len), dtype=torch.float32, device=device)
+        self._peer = None
+        if peer_copy and self.world > 1 and dist.get_backend(group) == "nccl":
+            self._peer = PeerCopyExchange.create(self, group, device)
+        if self._peer is not None:
+            self.full = self._peer.full
+        else:
+            self.full = torch.zeros((self.n, self.feat_len), dtype=torch.float32, device=device)
         self._own_full = True
+
+    @property
+    def exchange(self):
+        """'peer-copy' (copy engines over NVLink into the peers' buffers) or 'all-gather' (the backend's collective)."""
+        return "peer-copy" if self._peer is not None else "all-gather"
+
+    def _slot(self, p):
+        """Rows of the gather buffer that hold rank p's block."""
+        if self.padded:
+            return p * self.slot, p * self.slot + int(self.bounds[p + 1] - self.bounds[p])
+        return int(self.bounds[p]), int(self.bounds[p + 1])
 
     def gather(self, x_local):
         if self.world == 1:
             self.full = x_local  # nothing to exchange: the local rows are all rows
             self._own_full = False
+        elif self._peer is not None:
+            self.gather_async(x_local).wait()
         else:
             self._gather(self.full, x_local)
         return self
@@ -248,6 +267,9 @@ class GatheredFeatures(_ShardedBase):
         self._work = None
         if self.world == 1 or dist.get_backend(self.group) != "nccl":
             return self.gather(x_local)
+        if self._peer is not None:
+            self._peer_done = self._peer.start(x_local)
+            return self
         self._work = self._gather_async(self.full, x_local)
         return self
 
@@ -318,6 +340,10 @@ class GatheredFeatures(_ShardedBase):
         if copied is not None:  # world size 1: only the host copy to wait for
             torch.cuda.current_stream(self.device).wait_event(copied)
             self._copied = None
+        done = getattr(self, "_peer_done", None)
+        if done is not None:
+            torch.cuda.current_stream(self.device).wait_event(done)
+            self._peer_done = None
         work = getattr(self, "_work", None)
         if work is not None:
             try:
@@ -326,6 +352,86 @@ class GatheredFeatures(_ShardedBase):
                 raise ExchangeError("rank %d of %d: feature all-gather failed: %s" % (self.rank, self.world, exc)) from exc
             self._work = None
         return self
+
+
+# ---- the all-gather as copies by the copy engines ----------------------------------------------------------
+# A collective kernel that runs beside the compute kernels takes SMs from them for as long as it lasts.
+# The exchange itself needs none: every rank's gather buffer is allocated as symmetric memory (mapped into
+# every peer of the node), and a rank delivers its block with one plain device-to-device copy per peer -
+# work for the copy engines, over NVLink, into the peer's own memory.  Two one-element all-reduces on the
+# exchange stream order it against the peers: the first says "every rank's kernels have finished reading the
+# buffer's previous contents" (each rank enqueues it behind its own compute stream), the second "every rank's
+# copies have landed".  Nothing here waits in a kernel of this library; a peer that is gone shows up as the
+# process group's timeout on those all-reduces.
+class PeerCopyExchange:
+    """The gather buffer of one ``GatheredFeatures`` as symmetric memory, and the streams its copies run on."""
+
+    CHUNKS = 2  # pieces per peer, each on a stream of its own
+
+    @classmethod
+    def create(cls, owner, group, device):
+        """None where symmetric memory cannot be set up (the caller then uses the collective)."""
+        try:
+            return cls(owner, group, device)
+        except Exception:  # no symmetric-memory support in this torch build / on this node
+            return None
+
+    def __init__(self, owner, group, device):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.owner = owner
+        self.device = device
+        shape = (owner.n, owner.feat_len)
+        with torch.cuda.device(device):
+            self.full = symm.empty(shape, dtype=torch.float32, device=device)
+            self.full.zero_()
+            handle = symm.rendezvous(self.full, group)
+            self.peer_full = {p: handle.get_buffer(p, shape, torch.float32) for p in range(owner.world) if p != owner.rank}
+            self._handle = handle
+            self._token = torch.zeros(1, dtype=torch.float32, device=device)
+            self._stream = torch.cuda.Stream(device)
+            self._peer_streams = {p: [torch.cuda.Stream(device) for _ in range(self.CHUNKS)] for p in self.peer_full}
+        self._group = group
+
+    def _barrier(self):
+        """All ranks' exchange streams meet here (enqueued on the current stream)."""
+        try:
+            dist.all_reduce(self._token, group=self._group, async_op=True).wait()
+        except Exception as exc:
+            raise ExchangeError("rank %d of %d: feature exchange failed: %s" % (self.owner.rank, self.owner.world, exc)) from exc
+
+    def start(self, x_local):
+        """Enqueue the exchange behind the work the current stream holds; returns the event that marks the
+        gather buffer complete."""
+        o = self.owner
+        lo, hi = o._slot(o.rank)
+        if tuple(x_local.shape) != (hi - lo, o.feat_len):
+            raise ValueError("local block has shape %s, this rank owns %d rows of %d columns"
+                             % (tuple(x_local.shape), hi - lo, o.feat_len))
+        ex = self._stream
+        ex.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(ex):
+            self._barrier()  # every rank is past the last reader of its buffer
+            mine = self.full[lo:hi]
+            if mine.data_ptr() != x_local.data_ptr():
+                mine.copy_(x_local, non_blocking=True)
+            src = x_local.contiguous()
+            ready = ex.record_event()
+            # a copy engine moves one copy at a time: several pieces per peer keep more of them busy
+            cuts = [lo + (hi - lo) * c // self.CHUNKS for c in range(self.CHUNKS + 1)]
+            for c in range(self.CHUNKS):
+                a, b = cuts[c], cuts[c + 1]
+                if a == b:
+                    continue
+                for p, streams in self._peer_streams.items():
+                    st = streams[c]
+                    st.wait_event(ready)
+                    with torch.cuda.stream(st):
+                        self.peer_full[p][a:b].copy_(src[a - lo:b - lo], non_blocking=True)
+                    src.record_stream(st)
+                    ex.wait_stream(st)
+            self._barrier()  # every rank's copies have landed
+            return ex.record_event()
 
 
 # ---- exchanging only the rows a shard references ---------------------------------------------------------

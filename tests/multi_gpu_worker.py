@@ -72,6 +72,14 @@ def check_graph(graph, rank, world, device):
         g2 = GatheredFeatures(bounds, d, device=device)
         g2.gather_async(xl)
         np.testing.assert_array_equal(spmm.run(g2.wait()).cpu().numpy(), want)
+        # the exchange as copies into the peers' buffers (symmetric memory), twice: the second exchange must
+        # wait for the first one's readers on every rank before it overwrites
+        g4 = GatheredFeatures(bounds, d, device=device, peer_copy=True)
+        assert g4.exchange == "peer-copy", "symmetric memory could not be set up on this node"
+        for _ in range(2):
+            g4.gather_async(xl)
+            np.testing.assert_array_equal(spmm.run(g4.wait()).cpu().numpy(), want)
+            np.testing.assert_array_equal(sddmm.run(g4, yl).cpu().numpy(), e)
         want_e = oracle.sddmm(coo.row, coo.col, x, y)[adj.indptr[lo]:adj.indptr[hi]]
         np.testing.assert_allclose(e, want_e, rtol=1e-5, atol=1e-4)
         # host-buffer step: rows come from pinned host memory, results go back to it (twice: buffers reused)
