@@ -4,7 +4,9 @@ sweeps, same protocol (mean seconds of 5 back-to-back runs after a warm-up).  Bo
 the GPU here; 'x86' sweeps the x86 class's partition knobs, 'cuda' the CUDA class's launch knobs
 (accepted, no effect on results or, by design, on speed) plus the feature-tile width.
 
-Without --dataset a seeded synthetic graph is generated (--synthetic C0|C1|C2|C4).
+Without --dataset a seeded synthetic graph is generated (--synthetic C0|C1|C2|C4).  --shard R/W keeps
+only the rows that rank R of W owns (nnz-balanced contiguous ranges, all columns): what one GPU of a
+W-GPU run computes.
 """
 import argparse
 import os
@@ -66,6 +68,7 @@ if __name__ == '__main__':
     parser.add_argument("--synthetic", type=str, default="C0", help="named synthetic graph when no --dataset is given")
     parser.add_argument("--feat-len", type=int, default=128, help="The feature length")
     parser.add_argument("--target", type=str, default='cuda', choices=['x86', 'cuda'])
+    parser.add_argument("--shard", type=str, default=None, help="R/W: only the rows of rank R of W (nnz-balanced ranges)")
     args = parser.parse_args()
     if args.dataset:
         adj = scipy.sparse.load_npz(args.dataset)
@@ -75,4 +78,10 @@ if __name__ == '__main__':
     else:
         from featgraph_b200 import graphgen
         adj = graphgen.workload_graph(args.synthetic)
+    if args.shard:
+        from featgraph_b200.sharded import shard_csr_rows
+        from featgraph_b200.util import nnz_balanced_row_ranges
+        r, w = (int(v) for v in args.shard.split("/"))
+        adj = shard_csr_rows(adj, nnz_balanced_row_ranges(adj.indptr, w), r)
+        print("shard %d of %d: %d rows, %d nonzeros" % (r, w, adj.shape[0], adj.nnz))
     (bench_x86 if args.target == 'x86' else bench_cuda)(adj, args.feat_len)

@@ -273,6 +273,11 @@ def test_benchmark_scripts_read_npz_datasets(tmp_path):
                            timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
         assert "average time of 5 runs" in r.stdout
+    # one rank's rows of a several-GPU run
+    r = subprocess.run([sys.executable, "-m", "featgraph_b200.benchmark.bench_vanilla_spmm", "--dataset", csr_path,
+                        "--feat-len", "32", "--shard", "1/3"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "shard 1 of 3" in r.stdout and "average time of 5 runs" in r.stdout
 
 
 def test_sddmm_module_column_blocks(oracle):
