@@ -117,7 +117,10 @@ def _worker_layouts(rank, world, port, tmpdir):
         for bounds, padded in ((np.array([0, 140, 300]), True), (np.array([0, 10, 300]), False)):
             assert use_padded_layout(bounds) == padded
             lo, hi = int(bounds[rank]), int(bounds[rank + 1])
-            g = GatheredFeatures(bounds, d)
+            # peer_copy needs NCCL and symmetric memory: on other backends the collective is used
+            g = GatheredFeatures(bounds, d, peer_copy=padded)
+            assert g.exchange == "all-gather"
+            assert g._slot(rank) == ((rank * g.slot, rank * g.slot + hi - lo) if padded else (lo, hi))
             assert g.padded == padded and g.full.shape[0] == (2 * int(np.diff(bounds).max()) if padded else n)
             g.gather(torch.from_numpy(x[lo:hi].copy()))
             local = remap_columns(shard_csr_rows(adj, bounds, rank), bounds)
