@@ -370,28 +370,41 @@ class PeerCopyExchange:
 
     @classmethod
     def create(cls, owner, group, device):
-        """None where symmetric memory cannot be set up (the caller then uses the collective)."""
-        try:
-            return cls(owner, group, device)
-        except Exception:  # no symmetric-memory support in this torch build / on this node
-            return None
-
-    def __init__(self, owner, group, device):
-        import torch.distributed._symmetric_memory as symm
+        """None where symmetric memory cannot be set up on every rank (the caller then uses the collective).
+        The ranks agree on the outcome after each step, so that no rank waits in an exchange its peers do
+        not take part in."""
         group = group if group is not None else dist.group.WORLD
-        self.owner = owner
-        self.device = device
+        self = cls.__new__(cls)
+        self.owner, self.device, self._group = owner, device, group
+        self.error = None
+
+        def everyone(ok):
+            flag = torch.tensor([1.0 if ok else 0.0], dtype=torch.float32, device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            return bool(flag.item() > 0.5)
+
         shape = (owner.n, owner.feat_len)
-        with torch.cuda.device(device):
-            self.full = symm.empty(shape, dtype=torch.float32, device=device)
-            self.full.zero_()
-            handle = symm.rendezvous(self.full, group)
-            self.peer_full = {p: handle.get_buffer(p, shape, torch.float32) for p in range(owner.world) if p != owner.rank}
-            self._handle = handle
-            self._token = torch.zeros(1, dtype=torch.float32, device=device)
-            self._stream = torch.cuda.Stream(device)
-            self._peer_streams = {p: [torch.cuda.Stream(device) for _ in range(self.CHUNKS)] for p in self.peer_full}
-        self._group = group
+        try:
+            import torch.distributed._symmetric_memory as symm
+            with torch.cuda.device(device):
+                self.full = symm.empty(shape, dtype=torch.float32, device=device)
+                self.full.zero_()
+        except Exception as exc:  # no symmetric-memory support in this torch build, or no memory
+            self.error = exc
+        if not everyone(self.error is None):
+            return None
+        try:
+            with torch.cuda.device(device):
+                handle = symm.rendezvous(self.full, group)
+                self.peer_full = {p: handle.get_buffer(p, shape, torch.float32)
+                                  for p in range(owner.world) if p != owner.rank}
+                self._handle = handle
+                self._token = torch.zeros(1, dtype=torch.float32, device=device)
+                self._stream = torch.cuda.Stream(device)
+                self._peer_streams = {p: [torch.cuda.Stream(device) for _ in range(self.CHUNKS)] for p in self.peer_full}
+        except Exception as exc:  # the node cannot map peers' memory
+            self.error = exc
+        return self if everyone(self.error is None) else None
 
     def _barrier(self):
         """All ranks' exchange streams meet here (enqueued on the current stream)."""
