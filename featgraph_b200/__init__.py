@@ -9,7 +9,7 @@ __all__ = ["util", "module", "placeholder", "Placeholder"]
 def __getattr__(name):
     # the module layer needs torch; import it on first use so that the host-side
     # utilities stay importable on their own
-    if name in ("module", "op", "graphgen", "sharded"):
+    if name in ("module", "op", "graphgen", "sharded", "graph_capture"):
         import importlib
         return importlib.import_module("." + name, __name__)
     raise AttributeError(name)
