@@ -72,9 +72,11 @@ def parse_args():
     p.add_argument("--no-prefetch", action="store_true",
                    help="N > 1: exchange each feature matrix right before its ops instead of during the previous ones")
     p.add_argument("--no-cpu-baseline", action="store_true")
-    p.add_argument("--exchange", choices=("all-gather", "peer-copy"), default="all-gather",
-                   help="N > 1, device-timed steps: how the feature rows are exchanged - the backend's all-gather, or one "
-                        "device-to-device copy per peer into symmetric memory (copy engines, no SMs)")
+    p.add_argument("--exchange", choices=("auto", "collective", "peer"), default="auto",
+                   help="N > 1: how the feature rows are exchanged. collective: the backend's all-gather / all-to-all. "
+                        "peer: through symmetric memory - one device-to-device copy per peer (all-gather layouts; copy "
+                        "engines, no SMs), or each rank reading the rows it needs from its peers' memory (needed-rows "
+                        "layout). auto: peer for the needed-rows layout (C4), collective otherwise")
     p.add_argument("--all-gather", action="store_true",
                    help="C4 at N > 1: exchange whole feature matrices (all-gather) even where exchanging only the rows "
                         "each shard references would be chosen")
@@ -372,7 +374,7 @@ def run_ours(args):
     def exchange_buffer(d):
         if needed is not None:
             from featgraph_b200.sharded import NeededFeatures
-            return NeededFeatures(needed, d, device=device)
+            return NeededFeatures(needed, d, device=device, peer_pull=args.exchange in ("auto", "peer"))
         return GatheredFeatures(bounds, d, device=device)
 
     # features: generated whole (seeded), each rank keeps its rows; pinned host copies for e2e
@@ -395,12 +397,22 @@ def run_ours(args):
 
     # C2/C3: both ops of a step gather from the same feature matrix X_d, so it is exchanged once per
     # d and shared (GatheredFeatures); C4: X feeds SpMM, Y feeds SDDMM - two exchanges.
-    shared = {d: GatheredFeatures(bounds, d, device=device, peer_copy=args.exchange == "peer-copy") for d in dims} \
+    shared = {d: GatheredFeatures(bounds, d, device=device, peer_copy=args.exchange == "peer") for d in dims} \
         if WORKLOAD != "C4" else {}
-    exchange_kind = shared[dims[0]].exchange if shared else ("needed-rows" if needed is not None else "all-gather")
     # C4 at N > 1: Y is not needed before the SDDMM, so its exchange runs beside the SpMM
     c4_y = {d: exchange_buffer(d) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
     c4_x = {d: exchange_buffer(d) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
+    exchange_kind = shared[dims[0]].exchange if shared else \
+        ("needed-rows / " + c4_x[dims[0]].exchange if (needed is not None and c4_x) else "all-gather")
+    c4_pull = bool(c4_x) and getattr(c4_x[dims[0]], "exchange", "") == "peer-pull"
+    if c4_pull:
+        # the step's inputs live where the peers can read them (this rank's block of the symmetric buffers):
+        # resident before the timed region like every other input, and the exchange copies nothing locally
+        for d in dims:
+            for buf, t in ((c4_x[d], dev_feats[d][0]), (c4_y[d], dev_feats[d][1])):
+                buf.local_input.copy_(t)
+            dev_feats[d] = (c4_x[d].local_input, c4_y[d].local_input)
+        torch.cuda.synchronize(device)
 
     prefetch = world > 1 and WORKLOAD != "C4" and not args.no_prefetch
     c4_overlap = bool(c4_y) and not args.no_prefetch
@@ -440,9 +452,11 @@ def run_ours(args):
             if WORKLOAD == "C4" and world > 1:
                 # X's exchange, then (beside the SpMM, unless --no-prefetch) Y's
                 c4_x[d].gather_async(xd)
-                if c4_overlap:
+                if c4_overlap and not c4_pull:
                     c4_y[d].gather_async(yd)
                 gx = c4_x[d].wait()
+                if c4_overlap and c4_pull:
+                    c4_y[d].gather_async(yd)  # its reads start when X's have ended: beside the SpMM, not beside X
                 if ev:
                     ev[1].record(stream)
                 h = spmm.run(gx)
@@ -573,6 +587,9 @@ def run_ours(args):
                     s_in, _ = sharded.copy_streams(device)
                     xs, ys = c4_stage[d]
                     with torch.cuda.stream(s_in):
+                        for buf in (e2e_x[d], e2e_y[d]):  # peer-pull: the stage is the block the peers read from
+                            if getattr(buf, "local_input", None) is not None:
+                                buf.wait_writable()
                         xs.copy_(feats[d][0], non_blocking=True)
                         ys.copy_(feats[d][1], non_blocking=True)
                         e2e_x[d].gather_async(xs)
@@ -599,8 +616,10 @@ def run_ours(args):
             e2e_x = {d: exchange_buffer(d) for d in dims}
             if WORKLOAD == "C4":
                 e2e_y = {d: exchange_buffer(d) for d in dims}
-                c4_stage = {d: (torch.empty((hi - lo, d), device=device), torch.empty((hi - lo, d), device=device))
-                            for d in dims}
+                def stage(buf, d):
+                    own = getattr(buf, "local_input", None)
+                    return own if own is not None else torch.empty((hi - lo, d), device=device)
+                c4_stage = {d: (stage(e2e_x[d], d), stage(e2e_y[d], d)) for d in dims}
         elif WORKLOAD != "C4":
             # deferred calls must not share staging buffers: one module per (op, d) for the e2e leg
             from featgraph import placeholder as _ph

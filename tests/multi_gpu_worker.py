@@ -124,6 +124,17 @@ def check_graph(graph, rank, world, device):
         scale = max(float(np.abs(want_e2).max()), 1.0)
         np.testing.assert_allclose(e2.cpu().numpy(), want_e2, rtol=1e-5, atol=1e-4 * scale)
         np.testing.assert_array_equal(spmm2.run(xl).cpu().numpy(), want_h[lo:hi])  # the blocking form
+        # the same rows fetched by this rank's own kernel from its peers' memory (symmetric memory, NVLink loads)
+        px, py = NeededFeatures(rows, d, device=device, peer_pull=True), NeededFeatures(rows, d, device=device, peer_pull=True)
+        assert px.exchange == "peer-pull", "symmetric memory could not be set up on this node"
+        for _ in range(2):
+            px.gather_async(xl)
+            py.gather_async(yl)
+            h = spmm2.run(px.wait())
+            e3 = sddmm2.run(py.wait(), h)
+        np.testing.assert_array_equal(px.full.cpu().numpy(), gx.full.cpu().numpy())
+        np.testing.assert_array_equal(h.cpu().numpy(), want_h[lo:hi])
+        np.testing.assert_array_equal(e3.cpu().numpy(), e2.cpu().numpy())
 
 
 def check_full_size_shard(rank, world, device):
