@@ -3,8 +3,10 @@
 // When a graph's rows are spread over several GPUs, a shard's column ids reference only part of the
 // feature matrix (on an R-MAT graph a fraction of it).  Each rank then sends every peer just the rows
 // that peer asked for: this kernel packs them, in the peer's order, into one contiguous send buffer for
-// the all-to-all.  One warp per row, 128-bit copies; d % 4 == 0 and 16-byte aligned buffers take the
-// vector path, anything else a scalar one.
+// the all-to-all.  The same kernel serves the exchange without a sender: src is then a peer GPU's feature
+// block (symmetric memory mapped into this process) and the rank that needs the rows reads them itself over
+// NVLink - plain loads, 64 warps per SM each with 512 bytes in flight.  One warp per row, 128-bit copies;
+// d % 4 == 0 and 16-byte aligned buffers take the vector path, anything else a scalar one.
 #include "common.cuh"
 
 namespace {

@@ -315,7 +315,9 @@ int fg_edge_binary_f32(const int32_t* d_row, const int32_t* d_col, const float* 
  * Row gather: dst[i, :] = src[rows[i], :] for i < n_rows_out (int64 row ids on the device, trusted to be in
  * range).  Plumbing of the multi-GPU layer, which has no counterpart in the reference (its modules are
  * single-device, module/spmm.py:218): a rank packs the feature rows each peer's shard references into one
- * send buffer for an all-to-all, instead of every rank receiving every row.  Strides in floats (0 = d).
+ * send buffer for an all-to-all, instead of every rank receiving every row; or, the other way round, a rank
+ * fetches the rows it needs itself: d_src may be another GPU's memory mapped into this process (peer access
+ * over NVLink; the kernel reads it with plain loads), d_rows and d_dst this GPU's.  Strides in floats (0 = d).
  * -------------------------------------------------------------------------------------- */
 int fg_gather_rows_f32(const float* d_src, int64_t ld_src, const int64_t* d_rows, int64_t n_rows_out, int32_t d,
                        float* d_dst, int64_t ld_dst, void* stream);
