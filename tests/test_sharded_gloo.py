@@ -207,7 +207,12 @@ def _worker_needed_rows(rank, world, port, tmpdir):
         assert int(rows.recv_counts.sum()) == len(want_needed)
         assert needed_rows_pay(rows) in (True, False)
         # what this rank sends: for each peer, that peer's needed ids inside [lo, hi), in ascending order
-        feats = NeededFeatures(rows, d)
+        feats = NeededFeatures(rows, d, peer_pull=True)  # needs NCCL and symmetric memory: here the all-to-all is used
+        assert feats.exchange == "all-to-all" and feats.local_input is None
+        feats.wait_writable()  # nothing to wait for
+        # the request lists the peer-pull form reads with: needed ids as row numbers within their owners' blocks
+        owner = np.searchsorted(bounds[1:], rows.needed, side="right")
+        np.testing.assert_array_equal(rows.request_rows.numpy(), rows.needed - bounds[owner])
         for _ in range(2):  # twice: buffers are reused
             feats.gather(torch.from_numpy(x[lo:hi].copy()))
             np.testing.assert_array_equal(feats.full.numpy()[:rows.n_compact], x[want_needed])
