@@ -76,7 +76,8 @@ def parse_args():
                    help="N > 1: how the feature rows are exchanged. collective: the backend's all-gather / all-to-all. "
                         "peer: through symmetric memory - one device-to-device copy per peer (all-gather layouts; copy "
                         "engines, no SMs), or each rank reading the rows it needs from its peers' memory (needed-rows "
-                        "layout). auto: peer for the needed-rows layout (C4), collective otherwise")
+                        "layout). auto: peer for the needed-rows layout (C4) and, up to 4 GPUs, for the all-gather layouts; "
+                        "collective otherwise")
     p.add_argument("--all-gather", action="store_true",
                    help="C4 at N > 1: exchange whole feature matrices (all-gather) even where exchanging only the rows "
                         "each shard references would be chosen")
@@ -397,7 +398,10 @@ def run_ours(args):
 
     # C2/C3: both ops of a step gather from the same feature matrix X_d, so it is exchanged once per
     # d and shared (GatheredFeatures); C4: X feeds SpMM, Y feeds SDDMM - two exchanges.
-    shared = {d: GatheredFeatures(bounds, d, device=device, peer_copy=args.exchange == "peer") for d in dims} \
+    # copy-engine exchange where it was measured to pay (2 and 4 GPUs); at ~360 GB/s per GPU the largest exchange
+    # of a step would no longer hide behind the kernels of a 1/8 shard, so from 8 GPUs on the collective is used
+    peer_copy = args.exchange == "peer" or (args.exchange == "auto" and 1 < world <= 4)
+    shared = {d: GatheredFeatures(bounds, d, device=device, peer_copy=peer_copy) for d in dims} \
         if WORKLOAD != "C4" else {}
     # C4 at N > 1: Y is not needed before the SDDMM, so its exchange runs beside the SpMM
     c4_y = {d: exchange_buffer(d) for d in dims} if WORKLOAD == "C4" and world > 1 else {}
@@ -709,7 +713,7 @@ def run_ours(args):
                    "once per step and d, inside the timed region%s" % (world, ", the exchange for the next d running beside "
                    "the current d's kernels" if prefetch else
                                                   (", Y's exchange running beside the SpMM" if c4_overlap else "")) +
-                   ("; only the rows each shard references are exchanged (all-to-all)" if needed is not None else "")
+                   ("; only the rows each shard references are exchanged" if needed is not None else "")
                    if world > 1 else "single GPU",
                    "l2_policy": "inputs larger than L2 (CSR arrays %.0f MB per pass; 10 different kernels "
                                 "and feature matrices between repeats of any one)" % (8.0 * nnz / 1e6),
