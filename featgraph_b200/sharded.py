@@ -363,6 +363,16 @@ class GatheredFeatures(_ShardedBase):
 # buffer's previous contents" (each rank enqueues it behind its own compute stream), the second "every rank's
 # copies have landed".  Nothing here waits in a kernel of this library; a peer that is gone shows up as the
 # process group's timeout on those all-reduces.
+def _symmetric_memory():
+    """torch's symmetric-memory module, set up for plain peer mappings: the exchanges here only read and write
+    peers' buffers through ordinary pointers, so the buffers need not be bound to an NVLink multicast object as
+    well (one binding less to undo when a rank goes away)."""
+    import os
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    import torch.distributed._symmetric_memory as symm
+    return symm
+
+
 class PeerCopyExchange:
     """The gather buffer of one ``GatheredFeatures`` as symmetric memory, and the streams its copies run on."""
 
@@ -385,7 +395,7 @@ class PeerCopyExchange:
 
         shape = (owner.n, owner.feat_len)
         try:
-            import torch.distributed._symmetric_memory as symm
+            symm = _symmetric_memory()
             with torch.cuda.device(device):
                 self.full = symm.empty(shape, dtype=torch.float32, device=device)
                 self.full.zero_()
@@ -576,7 +586,7 @@ class PeerPullExchange:
         slot = int(np.diff(rows.bounds).max())  # the same size on every rank, as symmetric memory wants
         shape = (max(slot, 1), owner.feat_len)
         try:
-            import torch.distributed._symmetric_memory as symm
+            symm = _symmetric_memory()
             with torch.cuda.device(device):
                 self.local = symm.empty(shape, dtype=torch.float32, device=device)
                 self.local.zero_()
