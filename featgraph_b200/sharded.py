@@ -357,7 +357,7 @@ class GatheredFeatures(_ShardedBase):
 # ---- the all-gather as copies by the copy engines ----------------------------------------------------------
 # A collective kernel that runs beside the compute kernels takes SMs from them for as long as it lasts.
 # The exchange itself needs none: every rank's gather buffer is allocated as symmetric memory (mapped into
-# every peer of the node), and a rank delivers its block with one plain device-to-device copy per peer -
+# every peer of the node), and a rank delivers its block with plain device-to-device copies (CHUNKS per peer) -
 # work for the copy engines, over NVLink, into the peer's own memory.  Two one-element all-reduces on the
 # exchange stream order it against the peers: the first says "every rank's kernels have finished reading the
 # buffer's previous contents" (each rank enqueues it behind its own compute stream), the second "every rank's
