@@ -213,6 +213,11 @@ def _worker_needed_rows(rank, world, port, tmpdir):
         # the request lists the peer-pull form reads with: needed ids as row numbers within their owners' blocks
         owner = np.searchsorted(bounds[1:], rows.needed, side="right")
         np.testing.assert_array_equal(rows.request_rows.numpy(), rows.needed - bounds[owner])
+        # ... so that reading owner q's block at its part of the list fills this rank's compact buffer in order
+        cut = np.concatenate([[0], np.cumsum(rows.recv_counts)])
+        pulled = np.concatenate([x[bounds[q]:bounds[q + 1]][rows.request_rows.numpy()[cut[q]:cut[q + 1]]]
+                                 for q in range(world)])
+        np.testing.assert_array_equal(pulled, x[rows.needed])
         for _ in range(2):  # twice: buffers are reused
             feats.gather(torch.from_numpy(x[lo:hi].copy()))
             np.testing.assert_array_equal(feats.full.numpy()[:rows.n_compact], x[want_needed])
